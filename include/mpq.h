@@ -1,0 +1,135 @@
+/*
+ * libmpq -- block-quantised linear operators for NVIDIA B200 (sm_100a).
+ *
+ * C ABI.  Every entry point returns an int32 status (0 = MPQ_OK, negative =
+ * error), never throws, aborts or prints.  Pointers named *_host are host
+ * memory borrowed for the duration of the call; pointers named *_dev are
+ * device memory on the context's GPU.  Handles are owned by the library and
+ * released by their _destroy call.  "stream" is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream); forward calls only enqueue work.
+ *
+ * Reference interface replaced: none exists.  The makepad/makepad snapshot has
+ * no quantised-linear operator, tensor type or CUDA binding; its only AI code
+ * is an HTTP chat client (studio/src/ai_chat/ai_chat_manager.rs:778-967).  The
+ * shape of this boundary follows the reference's own FFI idiom instead: a
+ * run-time loader struct of typed extern "C" function pointers
+ * (platform/src/os/linux/module_loader.rs:5-41, egl_sys.rs:311-375), raw
+ * pointers plus lengths, #[repr(C)] plain structs (libc_sys.rs:41-44), and an
+ * accelerated routine checked against a scalar one (libs/zune-jpeg/src/idct.rs:49-127).
+ *
+ * Canonical (interchange) formats
+ *   Q4     codes  u8[N][K/2]    element 2j = low nibble of byte j, 2j+1 = high
+ *                               nibble; nibble = two's-complement int4 in [-8,7]
+ *          scales u16[N][K/32]  IEEE binary16 bits; block b covers k in [32b,32b+32)
+ *          value  w[n,k] = fp32(scale[n,k/32]) * fp32(code[n,k])     (exact in fp32)
+ *   NVFP4  codes  u8[R][K/2]    same nibble order; nibble = e2m1 (S.EE.M)
+ *          sf     u8[R][K/16]   e4m3 finite-only bits, non-negative
+ *          value  v[r,k] = fp32(e2m1) * fp32(e4m3) * tensor_scale
+ */
+#ifndef MPQ_H
+#define MPQ_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MPQ_OK                  0
+#define MPQ_ERR_INVALID_ARG    -1   /* null pointer, bad enum, bad handle */
+#define MPQ_ERR_SHAPE          -2   /* K not a multiple of the block size, sizes <= 0, shard does not divide */
+#define MPQ_ERR_ALIGN          -3   /* device pointer not 16-byte aligned */
+#define MPQ_ERR_CUDA           -4   /* a CUDA runtime/driver call failed; see mpq_last_error */
+#define MPQ_ERR_UNSUPPORTED    -5   /* device is not sm_100, or size beyond a stated maximum */
+#define MPQ_ERR_PEER_TIMEOUT   -6   /* a bounded device-side wait on a peer flag ran out */
+#define MPQ_ERR_STATE          -7   /* call order violated (e.g. exchange used before peers were attached) */
+
+#define MPQ_FMT_Q4     1
+#define MPQ_FMT_NVFP4  2
+
+#define MPQ_TP_NONE    0
+#define MPQ_TP_COLUMN  1   /* split output rows N of W (the columns of W^T) across ranks */
+#define MPQ_TP_ROW     2   /* split the reduction dimension K across ranks; partial outputs are summed */
+
+typedef struct mpq_context mpq_context;
+typedef struct mpq_weight mpq_weight;
+typedef struct mpq_exchange mpq_exchange;
+
+typedef struct mpq_device_info {
+    int32_t device;
+    int32_t sm_count;
+    int32_t cc_major, cc_minor;
+    int64_t l2_bytes;
+    int64_t total_mem_bytes;
+    int32_t sm_clock_khz, mem_clock_khz;
+} mpq_device_info;
+
+/* ---- context ------------------------------------------------------------ */
+/* One per (process, GPU).  Fails with MPQ_ERR_UNSUPPORTED on anything but
+ * compute capability 10.x: there is no fallback path. */
+int32_t mpq_context_create(int32_t device, mpq_context** out);
+int32_t mpq_context_destroy(mpq_context* ctx);
+int32_t mpq_context_info(const mpq_context* ctx, mpq_device_info* out);
+const char* mpq_status_string(int32_t status);
+/* Text of the last error recorded on this context (thread-compatible, not thread-safe). */
+const char* mpq_last_error(const mpq_context* ctx);
+/* Number of kernels this context has launched since creation. */
+int64_t mpq_context_launch_count(const mpq_context* ctx);
+
+/* ---- Q4 weights ---------------------------------------------------------- */
+/* Uploads the canonical arrays and repacks them on the GPU into the layout the
+ * kernels stream (16x64 tiles, one 16-byte word group per lane).  With
+ * tp_mode COLUMN the handle keeps rows [rank*N/world, (rank+1)*N/world); with
+ * ROW it keeps K-slice [rank*K/world, (rank+1)*K/world) (K/world must be a
+ * multiple of 32).  Pass tp_mode NONE, rank 0, world 1 for the whole matrix. */
+int32_t mpq_q4_weight_create(mpq_context* ctx, int64_t N, int64_t K,
+                             const uint8_t* codes_host, const uint16_t* scales_host,
+                             int32_t tp_mode, int32_t rank, int32_t world, mpq_weight** out);
+/* Same, from canonical arrays already on the device. */
+int32_t mpq_q4_weight_create_dev(mpq_context* ctx, int64_t N, int64_t K,
+                                 const uint8_t* codes_dev, const uint16_t* scales_dev, mpq_weight** out);
+
+/* ---- NVFP4 weights ------------------------------------------------------- */
+/* B is given as [N][K/2] codes (K contiguous per output column) and [N][K/16]
+ * e4m3 scales.  K must be a multiple of 128, N a multiple of 128. */
+int32_t mpq_nvfp4_weight_create(mpq_context* ctx, int64_t N, int64_t K,
+                                const uint8_t* codes_host, const uint8_t* sf_host,
+                                float tensor_scale, mpq_weight** out);
+
+/* ---- any weight ---------------------------------------------------------- */
+int32_t mpq_weight_shape(const mpq_weight* w, int64_t* N, int64_t* K, int32_t* fmt);
+/* Exact fp32 export [N][K] read back FROM THE DEVICE LAYOUT (the bit-exact
+ * criterion: proves the repack preserved every value). */
+int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, float* out_dev, void* stream);
+int64_t mpq_weight_device_bytes(const mpq_weight* w);
+int32_t mpq_weight_destroy(mpq_weight* w);
+
+/* ---- Q4 linear ----------------------------------------------------------- */
+/* Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
+ * row-major device arrays, 16-byte aligned.  Any M >= 1 (M <= 16 is one
+ * launch; larger M runs in slabs of 16 rows).  Finite inputs with |x| < 3e38
+ * are handled at any magnitude (each CTA renormalises its slice by a power
+ * of two); a non-finite x yields non-finite outputs in its row. */
+int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
+                              float* y_dev, void* stream);
+/* Convenience end-to-end call with HOST buffers: copies X up, runs, copies Y
+ * back and synchronises. */
+int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight* w, const float* x_host, int64_t M,
+                                   float* y_host);
+
+/* ---- NVFP4 GEMM ---------------------------------------------------------- */
+/* C[M][N] (bf16 bits, row-major) = bf16( tsA * tsB * sum_k A~[m,k] * B~[n,k] ).
+ * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; M a
+ * multiple of 128.  The activation scale factors are re-tiled on the GPU
+ * inside this call (counted in its time). */
+int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
+                               const uint8_t* a_codes_dev, const uint8_t* a_sf_dev, float a_tensor_scale,
+                               int64_t M, uint16_t* c_bf16_dev, void* stream);
+/* Exact fp32 export [R][K] of a canonical NVFP4 tensor on the device. */
+int32_t mpq_nvfp4_dequantize(mpq_context* ctx, int64_t R, int64_t K, const uint8_t* codes_dev,
+                             const uint8_t* sf_dev, float tensor_scale, float* out_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPQ_H */

