@@ -73,6 +73,10 @@ int32_t mpq_context_info(const mpq_context* ctx, mpq_device_info* out);
 const char* mpq_status_string(int32_t status);
 /* Text of the last error recorded on this context (thread-compatible, not thread-safe). */
 const char* mpq_last_error(const mpq_context* ctx);
+/* Reads the device-side status word (this synchronises with all prior work on
+ * the GPU).  MPQ_ERR_PEER_TIMEOUT if a bounded wait inside a kernel ran out
+ * since the last poll; the word is then cleared. */
+int32_t mpq_context_poll_status(mpq_context* ctx);
 /* Number of kernels this context has launched since creation. */
 int64_t mpq_context_launch_count(const mpq_context* ctx);
 
@@ -105,7 +109,9 @@ int64_t mpq_weight_device_bytes(const mpq_weight* w);
 int32_t mpq_weight_destroy(mpq_weight* w);
 
 /* ---- Q4 linear ----------------------------------------------------------- */
-/* Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
+/* Forward calls on one context share that context's scratch buffers: issue
+ * them in stream order (one stream per context at a time).
+ * Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
  * row-major device arrays, 16-byte aligned.  Any M >= 1 (M <= 16 is one
  * launch; larger M runs in slabs of 16 rows).  Finite inputs with |x| < 3e38
  * are handled at any magnitude (each CTA renormalises its slice by a power

@@ -34,6 +34,7 @@ SIGNATURES = {
     "mpq_status_string": (C.c_char_p, [_i32]),
     "mpq_last_error": (C.c_char_p, [_vp]),
     "mpq_context_launch_count": (_i64, [_vp]),
+    "mpq_context_poll_status": (_i32, [_vp]),
     "mpq_q4_weight_create": (_i32, [_vp, _i64, _i64, _vp, _vp, _i32, _i32, _i32, _pp]),
     "mpq_q4_weight_create_dev": (_i32, [_vp, _i64, _i64, _vp, _vp, _pp]),
     "mpq_nvfp4_weight_create": (_i32, [_vp, _i64, _i64, _vp, _vp, _f32, _pp]),

@@ -31,6 +31,15 @@ struct mpq_context {
     // staging for the *_host convenience calls (grown on demand)
     float *hx, *hy;
     size_t hx_bytes, hy_bytes;
+    // scratch of the streaming Q4 kernel: epoch-tagged partial tiles of row pair-tiles cut by a run
+    // boundary (two slots per warp), the epoch of the last launch, one status word
+    uint2* q4_partials;
+    int q4_partials_warps;
+    uint32_t q4_epoch;
+    int* q4_status;
+    bool q4_stream;           // use the streaming kernel where the activation fits in shared memory
+    int q4_group;             // chunks per bulk copy of the streaming kernel (2 or 4)
+    int q4_ctas;              // CTAs per SM the streaming kernel aims for
     Nvfp4Scratch fp4;
 };
 
@@ -42,6 +51,8 @@ struct mpq_weight {
     Nvfp4Dev fp4;
 };
 
+unsigned long long* g_trace = nullptr;
+extern "C" unsigned long long* mpq_debug_trace() { return g_trace; }
 static const uint32_t CTX_MAGIC = 0x4D505143u, W_MAGIC = 0x4D505157u;
 
 static int32_t fail(mpq_context* ctx, int32_t code, const char* fmt, ...)
@@ -96,6 +107,10 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->launches = 0;
     c->hx = c->hy = nullptr;
     c->hx_bytes = c->hy_bytes = 0;
+    c->q4_partials = nullptr;
+    c->q4_partials_warps = 0;
+    c->q4_epoch = 0;
+    c->q4_status = nullptr;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&c->prop, device) != cudaSuccess) {
         delete c;
         return MPQ_ERR_CUDA;
@@ -108,6 +123,12 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->pdl = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_VARIANT");
     c->q4_variant = (e && e[0] == '1') ? 1 : 0;
+    e = getenv("MPQ_Q4_STREAM");
+    c->q4_stream = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_GROUP");
+    c->q4_group = (e && e[0] == '2') ? 2 : 4;
+    e = getenv("MPQ_Q4_CTAS");
+    c->q4_ctas = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     *out = c;
     return MPQ_OK;
 }
@@ -118,6 +139,8 @@ extern "C" int32_t mpq_context_destroy(mpq_context* ctx)
     cudaSetDevice(ctx->device);
     cudaFree(ctx->hx);
     cudaFree(ctx->hy);
+    cudaFree(ctx->q4_partials);
+    cudaFree(ctx->q4_status);
     ctx->fp4.release();
     ctx->magic = 0;
     delete ctx;
@@ -161,23 +184,21 @@ static int32_t q4_build(mpq_context* ctx, int64_t Nfull, int64_t Kfull, const ui
     q.K = K;
     q.nrp = (int)((N + 31) / 32);
     q.nchunks = (int)((K + 63) / 64);
-    cudaError_t e = cudaMalloc(&q.codes, q.code_bytes());
-    if (e == cudaSuccess) e = cudaMalloc(&q.scales, q.scale_bytes());
+    q.nchunks = (q.nchunks + Q4_GROUP_PAD - 1) / Q4_GROUP_PAD * Q4_GROUP_PAD;   // a bulk-copy group never straddles a row pair-tile
+    cudaError_t e = cudaMalloc(&q.stream, q.bytes());
     if (e != cudaSuccess) {
-        cudaFree(q.codes);
         delete w;
-        return fail(ctx, MPQ_ERR_CUDA, "cudaMalloc of %zu weight bytes failed: %s", q.code_bytes() + q.scale_bytes(), cudaGetErrorString(e));
+        return fail(ctx, MPQ_ERR_CUDA, "cudaMalloc of %zu weight bytes failed: %s", q.bytes(), cudaGetErrorString(e));
     }
     int64_t words = (int64_t)q.nrp * q.nchunks * 256, halves = (int64_t)q.nrp * q.nchunks * 64;
     q4_repack_codes_kernel<<<(unsigned)((words + 255) / 256), 256>>>(codes_dev, Kfull, row0, k0, N, K, q.nrp, q.nchunks,
-                                                                      reinterpret_cast<uint32_t*>(q.codes));
+                                                                      reinterpret_cast<uint32_t*>(q.stream));
     q4_repack_scales_kernel<<<(unsigned)((halves + 255) / 256), 256>>>(scales_dev, Kfull / 32, row0, k0 / 32, N, K / 32, q.nrp,
-                                                                        q.nchunks, reinterpret_cast<uint16_t*>(q.scales));
+                                                                        q.nchunks, reinterpret_cast<uint16_t*>(q.stream));
     ctx->launches += 2;
     e = cudaDeviceSynchronize();
     if (e != cudaSuccess) {
-        cudaFree(q.codes);
-        cudaFree(q.scales);
+        cudaFree(q.stream);
         delete w;
         return fail(ctx, MPQ_ERR_CUDA, "Q4 repack failed: %s", cudaGetErrorString(e));
     }
@@ -262,15 +283,14 @@ extern "C" int32_t mpq_weight_shape(const mpq_weight* w, int64_t* N, int64_t* K,
 extern "C" int64_t mpq_weight_device_bytes(const mpq_weight* w)
 {
     if (!w_ok(w)) return -1;
-    return w->fmt == MPQ_FMT_Q4 ? (int64_t)(w->q4.code_bytes() + w->q4.scale_bytes()) : (int64_t)w->fp4.device_bytes();
+    return w->fmt == MPQ_FMT_Q4 ? (int64_t)w->q4.bytes() : (int64_t)w->fp4.device_bytes();
 }
 
 extern "C" int32_t mpq_weight_destroy(mpq_weight* w)
 {
     if (!w_ok(w)) return MPQ_ERR_INVALID_ARG;
     cudaSetDevice(w->device);
-    cudaFree(w->q4.codes);
-    cudaFree(w->q4.scales);
+    cudaFree(w->q4.stream);
     w->fp4.release();
     w->magic = 0;
     delete w;
@@ -287,8 +307,7 @@ extern "C" int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, 
     if (w->fmt == MPQ_FMT_Q4) {
         const Q4Dev& q = w->q4;
         int64_t words = (int64_t)q.nrp * q.nchunks * 256;
-        q4_dequant_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(q.codes),
-                                                                           reinterpret_cast<const uint16_t*>(q.scales), q.N, q.K,
+        q4_dequant_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(q.stream), q.N, q.K,
                                                                            q.nrp, q.nchunks, out_dev);
     } else {
         const Nvfp4Dev& f = w->fp4;
@@ -306,11 +325,11 @@ template <int MT, bool SUBN>
 static cudaError_t q4_launch_t(const Q4Launch& p, dim3 grid, size_t smem, bool pdl, cudaStream_t s)
 {
     auto kern = q4_linear_kernel<MT, SUBN>;
-    static size_t configured = 0;          // per instantiation; raising the limit is idempotent
-    if (smem > 48 * 1024 && smem > configured) {
+    static bool configured = false;        // per instantiation; static + dynamic shared memory may pass 48 KiB
+    if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(160 * 1024));
         if (e != cudaSuccess) return e;
-        configured = 160 * 1024;
+        configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -336,9 +355,122 @@ static cudaError_t q4_launch_t(const Q4Launch& p, dim3 grid, size_t smem, bool p
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+// Scratch of the streaming kernel, allocated on first use and kept for the context's life.
+static const int Q4S_MAX_WARPS = 32 * 1024;    // up to four CTAs of 8 warps on up to 1024 SMs
+static int32_t q4_stream_scratch(mpq_context* ctx, int warps)
+{
+    if (!ctx->q4_status) {
+        CU_TRY(ctx, cudaMalloc(&ctx->q4_status, sizeof(int)));
+        CU_TRY(ctx, cudaMemset(ctx->q4_status, 0, sizeof(int)));
+    }
+    if (ctx->q4_partials_warps < warps) {
+        CU_TRY(ctx, cudaDeviceSynchronize());          // nobody may still be using the old array
+        cudaFree(ctx->q4_partials);
+        ctx->q4_partials = nullptr;
+        ctx->q4_partials_warps = 0;
+        int n = std::max(warps, 4096);
+        size_t bytes = (size_t)n * 2 * 32 * 4 * sizeof(uint2);
+        CU_TRY(ctx, cudaMalloc(&ctx->q4_partials, bytes));
+        CU_TRY(ctx, cudaMemset(ctx->q4_partials, 0, bytes));      // tag 0 is never a launch's epoch
+        ctx->q4_partials_warps = n;
+    }
+    return MPQ_OK;
+}
+
+// The streaming kernel applies when M <= 4 and the staged activation plus a ring fit in shared memory.
+struct Q4StreamPlan { int depth, G, nx, ctas_per_sm; size_t smem; };
+static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4StreamPlan* pl)
+{
+    if (!ctx->q4_stream || M > 4) return false;
+    const int G = ctx->q4_group;
+    size_t nblk = (size_t)q.nchunks * 2;
+    size_t xbytes = nblk * (2 * M) * 64 + nblk * M * 16 + 8 * 8 * Q4_WARPS;
+    size_t stage = (size_t)Q4_WARPS * G * Q4_UNIT_BYTES;
+    int need = (M * q.nchunks + 15) / 16;                 // float4 of x per thread
+    pl->G = G;
+    pl->nx = need <= 4 ? 4 : need <= 12 ? 12 : need <= 28 ? 28 : 0;
+    const int max_ctas = pl->nx == 28 ? 1 : ctx->q4_ctas;
+    // deepest ring that still lets max_ctas CTAs share an SM; else fewer CTAs
+    for (int ctas = max_ctas; ctas >= 1; --ctas) {
+        size_t budget = (size_t)(227 * 1024) / ctas - 10 * 1024;      // static shared memory (8.2 KiB) + 1 KiB the system reserves per CTA
+        for (int d = 4; d >= 2; --d) {
+            size_t total = stage * d + xbytes;
+            if (total <= budget && (ctas > 1 || d >= 2)) { pl->depth = d; pl->smem = total; pl->ctas_per_sm = ctas; return true; }
+        }
+    }
+    return false;
+}
+
+template <bool SUBN, int G, int NX, int MINB>
+static cudaError_t q4_stream_launch_t(const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
+{
+    auto kern = q4_stream_kernel<SUBN, G, NX, MINB>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(217 * 1024));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(Q4_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+template <bool SUBN, int G>
+static cudaError_t q4_stream_launch_nx(int nx, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
+{
+    switch (nx) {
+        case 4: return q4_stream_launch_t<SUBN, G, 4, 2>(p, grid, smem, pdl, s);
+        case 12: return q4_stream_launch_t<SUBN, G, 12, 2>(p, grid, smem, pdl, s);
+        case 28: return q4_stream_launch_t<SUBN, G, 28, 1>(p, grid, smem, pdl, s);
+        default: return q4_stream_launch_t<SUBN, G, 0, 2>(p, grid, smem, pdl, s);
+    }
+}
+
 // One launch for a slab of M <= 16 activation rows.
 static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
 {
+    Q4StreamPlan pl;
+    if (q4_stream_plan(ctx, q, M, &pl)) {
+        const int sms = ctx->prop.multiProcessorCount;
+        const int groups = (int)(q.units() / pl.G);
+        int W = (int)std::min<int64_t>((int64_t)sms * Q4_WARPS * pl.ctas_per_sm, groups);
+        W = std::min(W, Q4S_MAX_WARPS);
+        int32_t st = q4_stream_scratch(ctx, W);
+        if (st) return st;
+        if (++ctx->q4_epoch == 0) ctx->q4_epoch = 1;
+        Q4StreamLaunch p;
+        p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
+        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
+        p.partials = ctx->q4_partials; p.epoch = ctx->q4_epoch; p.status = ctx->q4_status;
+        { const char* d = getenv("MPQ_DBG"); p.dbg = d ? atoi(d) : 0; }
+        {
+            static unsigned long long* trace = nullptr;
+            static int trace_n = 0;
+            p.trace = nullptr;
+            if (getenv("MPQ_TRACE")) {
+                if (!trace) cudaMallocManaged(&trace, (size_t)64 * 1024 * 8 * 8);
+                p.trace = trace + (size_t)(trace_n++ % 64) * 1024 * 8;
+                g_trace = trace;
+            }
+        }
+        int grid = (W + Q4_WARPS - 1) / Q4_WARPS;
+        cudaError_t e;
+        const bool subn = ctx->q4_variant == 0;
+        if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
+        else e = subn ? q4_stream_launch_nx<true, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
+        ctx->launches += 1;
+        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
+        return MPQ_OK;
+    }
     const int MT = M <= 4 ? 1 : (M <= 8 ? 2 : 4);
     const int sms = ctx->prop.multiProcessorCount;
     // K split across a thread-block cluster until the grid covers the machine about three times
@@ -351,7 +483,7 @@ static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x,
     size_t smem = per_chunk * cpp;
 
     Q4Launch p;
-    p.codes = q.codes; p.scales = q.scales; p.X = x; p.Y = y;
+    p.stream = q.stream; p.X = x; p.Y = y;
     p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
     p.nchunks = q.nchunks; p.chunks_per_cta = cpc; p.chunks_per_phase = cpp; p.splits = splits;
     dim3 grid((unsigned)q.nrp, (unsigned)splits);
@@ -421,6 +553,18 @@ extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight
     CU_TRY(ctx, cudaMemcpyAsync(y_host, ctx->hy, yb, cudaMemcpyDeviceToHost, 0));
     CU_TRY(ctx, cudaStreamSynchronize(0));
     return MPQ_OK;
+}
+
+extern "C" int32_t mpq_context_poll_status(mpq_context* ctx)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!ctx->q4_status) return MPQ_OK;
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    int v = 0;
+    CU_TRY(ctx, cudaMemcpy(&v, ctx->q4_status, sizeof(int), cudaMemcpyDeviceToHost));   // synchronises with prior work
+    if (v == 0) return MPQ_OK;
+    cudaMemset(ctx->q4_status, 0, sizeof(int));         // a wait ran out: clear the word for the next launch
+    return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (code %d)", v);
 }
 
 // ---------------------------------------------------------------------------

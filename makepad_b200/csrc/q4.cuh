@@ -7,9 +7,9 @@
 //
 // DEVICE LAYOUT ("tile stream").  Rows are padded to a multiple of 32 and K to
 // a multiple of 64.  A *unit* is one row pair-tile (32 rows = two m16 tiles) by
-// one 64-wide K chunk:
-//   codes  1024 B per unit = tile0 (512 B) then tile1 (512 B); inside a tile
-//          lane l = 4g+t owns the 16 bytes at l*16 = words q0..q3, one word per
+// one 64-wide K chunk, stored as 1152 contiguous bytes: tile0 codes (512 B),
+// tile1 codes (512 B), scales (128 B):
+//   codes  inside a tile lane l = 4g+t owns the 16 bytes at l*16 = words q0..q3, one word per
 //          m16n8k16 MMA of the chunk.  Nibble i of word qj holds the OFFSET code
 //          n = code+8 of
 //              row  = tile*16 + g + 8*(i&1)
@@ -17,10 +17,11 @@
 //          so that (w & 0x000F000F), (w & 0x00F000F0), ((w>>8) & 0x000F000F),
 //          ((w>>8) & 0x00F000F0) are, as half2 bit patterns, exactly the four
 //          A-fragment registers of mma.m16n8k16 (rows g / g+8, k 2t..2t+1 / +8).
-//   scales 128 B per unit: lane group g owns 16 B = 8 halves
+//   scales lane group g owns 16 B = 8 halves
 //          [tile][row g | row g+8][block 0 | block 1].
-// Units are ordered (row pair, chunk), so one warp step reads 1 KiB + 128 B of
-// contiguous memory and eight warps of a CTA read 9 KiB contiguous.
+// Units are ordered (row pair, chunk): the whole matrix is ONE contiguous
+// stream, and any run of units is a contiguous byte range that a bulk copy
+// (cp.async.bulk) can bring into shared memory.
 //
 // ARITHMETIC.  The masked words are fp16 SUBNORMALS n*2^-24 (rows g) and
 // 16n*2^-24 (rows g+8): no conversion instruction is spent on the weights.
@@ -42,11 +43,13 @@ struct Q4Dev {
     int64_t N = 0, K = 0;      // logical shape of this (shard of the) matrix
     int nrp = 0;               // row pair-tiles  = ceil(N/32)
     int nchunks = 0;           // 64-wide K chunks = ceil(K/64)
-    uint4* codes = nullptr;    // nrp*nchunks*1024 B
-    uint4* scales = nullptr;   // nrp*nchunks*128 B
-    size_t code_bytes() const { return (size_t)nrp * nchunks * 1024; }
-    size_t scale_bytes() const { return (size_t)nrp * nchunks * 128; }
+    uint4* stream = nullptr;   // nrp*nchunks units of Q4_UNIT_BYTES
+    int64_t units() const { return (int64_t)nrp * nchunks; }
+    size_t bytes() const { return (size_t)nrp * nchunks * 1152; }
 };
+
+constexpr int Q4_UNIT_BYTES = 1152;
+constexpr int Q4_UNIT_U4 = Q4_UNIT_BYTES / 16;   // 72 uint4 per unit: 32 + 32 codes, 8 scales
 
 constexpr int Q4_WARPS = 8;
 constexpr int Q4_THREADS = Q4_WARPS * 32;
@@ -81,7 +84,7 @@ __global__ void q4_repack_codes_kernel(const uint8_t* __restrict__ codes, int64_
         }
         word |= n << (4 * i);
     }
-    out[W] = word;
+    out[unit * (Q4_UNIT_BYTES / 4) + (W & 255)] = word;
 }
 
 __global__ void q4_repack_scales_kernel(const uint16_t* __restrict__ scales, int64_t KBfull, int64_t row0, int64_t kb0,
@@ -96,12 +99,12 @@ __global__ void q4_repack_scales_kernel(const uint16_t* __restrict__ scales, int
     int64_t rp = unit / nchunks;
     int64_t row = rp * 32 + tile * 16 + g + 8 * rowsel;
     int64_t b = (int64_t)ch * 2 + blk;
-    out[H] = (row < N && b < KB) ? scales[(row0 + row) * KBfull + kb0 + b] : (uint16_t)0;
+    out[unit * (Q4_UNIT_BYTES / 2) + 512 + (H & 63)] = (row < N && b < KB) ? scales[(row0 + row) * KBfull + kb0 + b] : (uint16_t)0;
 }
 
 // exact fp32 export from the tile stream: out[row][k] = fp32(scale) * fp32(code)
-__global__ void q4_dequant_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ scales,
-                                  int64_t N, int64_t K, int nrp, int nchunks, float* __restrict__ out)
+__global__ void q4_dequant_kernel(const uint32_t* __restrict__ stream, int64_t N, int64_t K, int nrp, int nchunks,
+                                  float* __restrict__ out)
 {
     int64_t W = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)nrp * nchunks * 256;
@@ -111,7 +114,8 @@ __global__ void q4_dequant_kernel(const uint32_t* __restrict__ codes, const uint
     int ch = (int)(unit % nchunks);
     int64_t rp = unit / nchunks;
     int g = lane >> 2, t = lane & 3;
-    uint32_t word = codes[W];
+    uint32_t word = stream[unit * (Q4_UNIT_BYTES / 4) + (W & 255)];
+    const uint16_t* scales = reinterpret_cast<const uint16_t*>(stream + unit * (Q4_UNIT_BYTES / 4)) + 512;
     int blk = j >> 1;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -119,7 +123,7 @@ __global__ void q4_dequant_kernel(const uint32_t* __restrict__ codes, const uint
         int64_t row = rp * 32 + tile * 16 + g + 8 * rowsel;
         int64_t k = (int64_t)ch * 64 + 16 * j + 2 * t + (i >> 2) + 8 * ((i >> 1) & 1);
         if (row < N && k < K) {
-            uint16_t sb = scales[unit * 64 + g * 8 + tile * 4 + rowsel * 2 + blk];
+            uint16_t sb = scales[g * 8 + tile * 4 + rowsel * 2 + blk];
             float s = __half2float(__ushort_as_half(sb));
             int code = (int)((word >> (4 * i)) & 0xF) - 8;
             out[row * K + k] = s * (float)code;
@@ -141,7 +145,7 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p)
 __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
                                          float c0, float c1, float c2, float c3)
 {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
 }
@@ -175,8 +179,7 @@ __device__ __forceinline__ void q4_unpack(uint32_t w, uint32_t (&a)[4])
 }
 
 struct Q4Launch {
-    const uint4* codes;
-    const uint4* scales;
+    const uint4* stream;
     const float* X;        // [M][K]
     float* Y;              // [M][ldy]
     int M, N, K;
@@ -193,7 +196,7 @@ struct Q4Launch {
 template <int MT, bool SUBN>
 __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float red[Q4_WARPS][4 * MT][32];
     __shared__ float part[4 * MT][32];
     __shared__ uint32_t s_max[Q4_WARPS];
@@ -206,8 +209,8 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
     uint4* xs = reinterpret_cast<uint4*>(smem_raw);
     float4* cs = reinterpret_cast<float4*>(smem_raw + (size_t)cpp * 2 * ncols * 64);
 
-    const uint4* wbase = p.codes + ((size_t)blockIdx.x * p.nchunks) * 64 + lane;   // + chunk*64 (+32 for tile 1)
-    const uint4* sbase = p.scales + ((size_t)blockIdx.x * p.nchunks) * 8 + g;      // + chunk*8
+    const uint4* wbase = p.stream + ((size_t)blockIdx.x * p.nchunks) * Q4_UNIT_U4 + lane;   // + chunk*72 (+32 for tile 1)
+    const uint4* sbase = wbase - lane + 64 + g;                                             // + chunk*72
 
     float acc[2][MT][2];      // [tile][btile][row g | row g+8], summed over phases (already un-normalised)
 #pragma unroll
@@ -231,9 +234,9 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
         for (int s = 0; s < Q4_PF; ++s) {
             int c = ph0 + warp + s * Q4_WARPS;
             if (c < ph1) {
-                wq[s][0] = ldg_stream(wbase + (size_t)c * 64);
-                wq[s][1] = ldg_stream(wbase + (size_t)c * 64 + 32);
-                sq[s] = ldg_stream(sbase + (size_t)c * 8);
+                wq[s][0] = ldg_stream(wbase + (size_t)c * Q4_UNIT_U4);
+                wq[s][1] = ldg_stream(wbase + (size_t)c * Q4_UNIT_U4 + 32);
+                sq[s] = ldg_stream(sbase + (size_t)c * Q4_UNIT_U4);
             }
         }
         if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }
@@ -333,9 +336,9 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
                     uint4 w0 = wq[s][0], w1 = wq[s][1], sv = sq[s];
                     const int cn = c + Q4_WARPS * Q4_PF;
                     if (cn < ph1) {
-                        wq[s][0] = ldg_stream(wbase + (size_t)cn * 64);
-                        wq[s][1] = ldg_stream(wbase + (size_t)cn * 64 + 32);
-                        sq[s] = ldg_stream(sbase + (size_t)cn * 8);
+                        wq[s][0] = ldg_stream(wbase + (size_t)cn * Q4_UNIT_U4);
+                        wq[s][1] = ldg_stream(wbase + (size_t)cn * Q4_UNIT_U4 + 32);
+                        sq[s] = ldg_stream(sbase + (size_t)cn * Q4_UNIT_U4);
                     }
                     const int lb = (c - ph0) * 2;
                     uint4 bf[MT][2];
@@ -423,6 +426,463 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
             if (m < M && n < p.N) p.Y[(size_t)m * p.ldy + n] = part[m][r];
         }
     }
+}
+
+
+// ---------------------------------------------------------------------------
+// the streaming kernel: M <= 4, whole x resident in shared memory
+// ---------------------------------------------------------------------------
+// Eight warps per CTA, no CTA-wide synchronisation after the activation has been
+// staged.  The unit stream is cut into W equal contiguous runs of GROUPS (G
+// consecutive chunks of one row pair-tile; the layout pads K so that a group
+// never straddles a tile), one run per warp.  Each warp owns a private ring of
+// shared-memory stages that its lane 0 keeps full with cp.async.bulk copies
+// (mbarrier complete_tx), so the HBM stream of a warp never waits for its
+// arithmetic and -- because the first copies are issued BEFORE
+// griddepcontrol.wait -- not for the previous kernel in the stream either.
+// A row pair-tile that lies wholly inside one warp's run is written straight
+// to y.  A tile shared by warps of one CTA is summed through shared memory, in
+// warp order, when the CTA has drained its runs.  A tile cut by the boundary
+// between two CTAs is finished through global scratch (q4s_cross_cta).
+constexpr int Q4_GROUP_PAD = 4;                  // chunks per row pair-tile are padded to a multiple of this
+constexpr uint32_t Q4S_SPIN_LIMIT = 1u << 22;    // polls of one mbarrier before giving up
+
+struct Q4StreamLaunch {
+    const uint4* stream;
+    const float* X;         // [M][K]
+    float* Y;               // [M][ldy]
+    int M, N, K;
+    int64_t ldy;
+    int nchunks;            // per row pair-tile, a multiple of G
+    int groups;             // nrp * nchunks / G
+    int warps_total;        // W: warps that own a run (<= 8*gridDim.x, <= groups)
+    int depth;              // ring stages per warp
+    uint2* partials;        // [CTAs][2][32 lanes][4] (value, epoch) pairs
+    uint32_t epoch;         // this launch's tag: differs from every earlier launch on the same scratch
+    int* status;            // set non-zero when a bounded wait ran out
+    int dbg;
+    unsigned long long* trace;   // debug: [gridDim.x][8] timestamps of warp 0, or null
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// bounded wait on a phase parity: returns false when the limit ran out (the caller records it and leaves)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "WAIT_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra WAIT_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 p, n, %3;\n\t"
+        "@p bra WAIT_LOOP;\n\t"
+        "mov.u32 %0, 0;\n\t"
+        "bra WAIT_END;\n\t"
+        "WAIT_DONE:\n\t"
+        "mov.u32 %0, 1;\n\t"
+        "WAIT_END:\n\t"
+        "}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(limit) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ int q4s_run_start(int i, int groups, int W) { return (int)(((int64_t)i * groups) / W); }
+// index of the warp whose run contains group gidx
+__device__ __forceinline__ int q4s_owner(int gidx, int groups, int W)
+{
+    int i = (int)(((int64_t)gidx * W) / groups);
+    while (i + 1 < W && q4s_run_start(i + 1, groups, W) <= gidx) ++i;
+    while (i > 0 && q4s_run_start(i, groups, W) > gidx) --i;
+    return i;
+}
+
+__device__ __forceinline__ void st_tagged(uint2* p, float v, uint32_t tag)
+{
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const uint2* p)
+{
+    uint2 r;
+    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+
+// Write one finished row pair-tile to y.  v[tile*2+h] belongs to row tile*16 + g + 8h, activation row t.
+__device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const float (&v)[4], int rp, int lane)
+{
+    const int g = lane >> 2, t = lane & 3;
+    if (t < p.M) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            int n = rp * 32 + (q >> 1) * 16 + g + 8 * (q & 1);
+            if (n < p.N) p.Y[(size_t)t * p.ldy + n] = v[q];
+        }
+    }
+}
+
+// A row pair-tile cut by the boundary between two CTAs' runs.  Every CTA but the first that shares
+// the tile stores its partial as (value, epoch) pairs -- one aligned 8-byte store each, so a reader
+// that sees the epoch sees the value, with no fence and no counter -- and carries on.  The first CTA,
+// for which the tile is the END of its run, polls the others' slots (bounded), adds them in CTA
+// order, so the sum does not depend on timing, and writes y.
+__device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4], int rp, int r0, int r1, int cta_first_rp,
+                                           int lane)
+{
+    const int W = p.warps_total;
+    const int c0 = q4s_owner(r0, p.groups, W) / Q4_WARPS;
+    if ((int)blockIdx.x != c0) {
+        uint2* mine = p.partials + (((size_t)blockIdx.x * 2 + (rp == cta_first_rp ? 0 : 1)) * 32 + lane) * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], p.epoch);
+        return;
+    }
+    const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4_WARPS;
+    // every later CTA starts its run inside this tile, so the tile is its first one (slot 0)
+    const uint2* src = p.partials + (((size_t)(c0 + 1) * 2) * 32 + lane) * 4;
+    for (int c = c0 + 1; c <= c1; c += 4) {                // four contributors' loads in flight at a time
+        uint2 r[4][4];
+        bool ok = false;
+        for (uint32_t spin = 0; spin < Q4S_SPIN_LIMIT && !ok; ++spin) {
+            ok = true;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    r[u][q] = (c + u <= c1) ? ld_tagged(src + (size_t)u * 256 + q) : make_uint2(0u, p.epoch);
+                    ok = ok && (r[u][q].y == p.epoch);
+                }
+            ok = __all_sync(0xFFFFFFFFu, ok);
+        }
+        if (!ok) {
+            if (lane == 0) atomicExch(p.status, 2);
+            return;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] += __uint_as_float(r[u][q].x);
+        src += 4 * 256;
+    }
+    q4s_store_tile(p, v, rp, lane);
+}
+
+// One float4 of x -> normalised hi/lo fp16 fragments in xs, block corrections in cs.
+//   xs: uint4 [chunk][2M columns][4 t][2 blocks]   column 2m = hi, 2m+1 = lo of activation row m; the uint4 of
+//                                                  lane t holds halves [j0: k 2t,2t+1 | j0: k 2t+8,2t+9 | j1 ...]
+//   cs: float4[chunk][M][2 blocks]                 (c_hi, c_lo, 16 c_hi, 16 c_lo): the MMA's C operand
+template <bool SUBN>
+__device__ __forceinline__ void q4s_stage_one(float4 v, bool on, int m, int f, float sc, int M, int ncols, uint4* xs,
+                                              float4* cs, int lane)
+{
+    float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
+    __half hi[4], lo[4];
+    float shi = 0.f, slo = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        hi[q] = __float2half_rn(e[q]);
+        float hf = __half2float(hi[q]);
+        lo[q] = __float2half_rn(e[q] - hf);
+        shi += hf;
+        slo += __half2float(lo[q]);
+    }
+    const int kk = 4 * f, chunk = kk >> 6, blk = (kk >> 5) & 1;
+    if (on) {
+        int jj = (kk >> 4) & 1, slot = kk & 15;
+        int tt0 = (slot & 7) >> 1, up = slot >> 3;
+        __half2* dst = reinterpret_cast<__half2*>(xs + ((size_t)chunk * ncols + 2 * m) * 8);   // 8 uint4 per column
+        int w0 = (tt0 * 2 + blk) * 4 + jj * 2 + up, w1 = ((tt0 + 1) * 2 + blk) * 4 + jj * 2 + up;
+        dst[w0] = __halves2half2(hi[0], hi[1]);
+        dst[w1] = __halves2half2(hi[2], hi[3]);
+        dst[32 + w0] = __halves2half2(lo[0], lo[1]);     // next column (lo): 8 uint4 = 32 half2 further
+        dst[32 + w1] = __halves2half2(lo[2], lo[3]);
+    }
+    if (SUBN) {
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {                  // 8 consecutive lanes cover one 32-block of one row
+            shi += __shfl_xor_sync(0xFFFFFFFFu, shi, o);
+            slo += __shfl_xor_sync(0xFFFFFFFFu, slo, o);
+        }
+        if (on && (lane & 7) == 0) {
+            const float k8 = -8.f * 5.9604644775390625e-8f;     // -8 * 2^-24
+            float ch = k8 * shi, cl = k8 * slo;
+            cs[((size_t)chunk * M + m) * 2 + blk] = make_float4(ch, cl, 16.f * ch, 16.f * cl);
+        }
+    }
+}
+
+// dynamic shared memory: ring [8 warps][depth][G units] | xs | cs | mbarriers
+// NX = float4 of x each thread keeps in registers between the max pass and the conversion pass
+//      (0: re-read x from global memory instead, for activations too long for the register file).
+template <bool SUBN, int G, int NX, int MINB>
+__global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4StreamLaunch p)
+{
+    constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ uint32_t s_max[Q4_WARPS];
+    __shared__ float wpart[Q4_WARPS][2][4][32];   // each warp's partial first / last tile, [q][lane]
+    __shared__ int wrp[Q4_WARPS][2];              // the tile index of each, -1 if none
+    __shared__ uint4 zero_pg[2];                  // what lanes outside the 2M real columns read
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int M = p.M, ncols = 2 * M, nblk = p.nchunks * 2, D = p.depth;
+    if (lane < 2) wrp[warp][lane] = -1;
+    if (tid < 2) zero_pg[tid] = make_uint4(0, 0, 0, 0);
+#define Q4S_TRACE(slot)                                                                         \
+    if (p.trace && tid == 0) {                                                                  \
+        unsigned long long t_;                                                                  \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+        p.trace[(size_t)blockIdx.x * 8 + (slot)] = t_;                                          \
+    }
+    Q4S_TRACE(0)
+    unsigned char* ring = smem_raw + (size_t)warp * D * STAGE_BYTES;
+    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)Q4_WARPS * D * STAGE_BYTES);
+    float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nblk * ncols * 64);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)nblk * M * 16) + warp * 8;
+
+    const int W = p.warps_total;
+    const int gw = blockIdx.x * Q4_WARPS + warp;
+    const bool active = gw < W;
+    const int gb = active ? q4s_run_start(gw, p.groups, W) : 0;
+    const int ge = active ? q4s_run_start(gw + 1, p.groups, W) : 0;
+    const int ngroups = ge - gb;
+    const unsigned char* gnext = reinterpret_cast<const unsigned char*>(p.stream) + (size_t)gb * STAGE_BYTES;
+    const uint32_t ring_u32 = smem_u32(ring), bars_u32 = smem_u32(bars);
+
+    if (lane == 0) {
+        for (int s = 0; s < D; ++s) mbar_init(&bars[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    int issued = 0;
+    if (lane == 0) {
+        const int first = min(D, ngroups);
+        for (; issued < first; ++issued) {
+            mbar_expect_tx(bars_u32 + issued * 8, STAGE_BYTES);
+            bulk_g2s(ring_u32 + issued * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + issued * 8);
+            gnext += STAGE_BYTES;
+        }
+    }
+
+    Q4S_TRACE(1)
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    Q4S_TRACE(2)
+
+    // ---- stage all of x as normalised hi/lo fp16 B fragments (same scheme as q4_linear_kernel)
+    const int pk4 = p.nchunks * 16;                       // float4 per activation row, padding included
+    const int total4 = (p.dbg & 1) ? 0 : M * pk4;
+    float4 xv[NX > 0 ? NX : 1];
+    uint32_t mx = 0;
+    if (NX > 0) {
+#pragma unroll
+        for (int it = 0; it < NX; ++it) {
+            int i = it * Q4_THREADS + tid;
+            int m = i / pk4, f = i - m * pk4;
+            xv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < total4 && 4 * f < p.K) xv[it] = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
+        }
+#pragma unroll
+        for (int it = 0; it < NX; ++it) {
+            mx = max(mx, __float_as_uint(xv[it].x) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(xv[it].y) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(xv[it].z) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(xv[it].w) & 0x7FFFFFFFu);
+        }
+    } else {
+        for (int i = tid; i < total4; i += Q4_THREADS) {
+            int m = i / pk4, f = i - m * pk4;
+            if (4 * f < p.K) {
+                float4 v = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
+                mx = max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu);
+                mx = max(mx, __float_as_uint(v.y) & 0x7FFFFFFFu);
+                mx = max(mx, __float_as_uint(v.z) & 0x7FFFFFFFu);
+                mx = max(mx, __float_as_uint(v.w) & 0x7FFFFFFFu);
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if (lane == 0) s_max[warp] = mx;
+    __syncthreads();
+    mx = s_max[0];
+#pragma unroll
+    for (int w = 1; w < Q4_WARPS; ++w) mx = max(mx, s_max[w]);
+    int emax = (int)(mx >> 23);
+    float sc = 1.f, inv_sc = 1.f;
+    if (mx != 0 && emax < 255) {
+        emax = max(emax, 16);
+        sc = __uint_as_float((uint32_t)(268 - emax) << 23);
+        inv_sc = __uint_as_float((uint32_t)(emax - 14) << 23);
+    }
+    if (NX > 0) {
+#pragma unroll
+        for (int it = 0; it < NX; ++it) {
+            int i = it * Q4_THREADS + tid;
+            bool on = i < total4;
+            int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
+            q4s_stage_one<SUBN>(xv[it], on, m, f, sc, M, ncols, xs, cs, lane);
+        }
+    } else {
+        const int iters = (total4 + Q4_THREADS - 1) / Q4_THREADS;
+        for (int it = 0; it < iters; ++it) {
+            int i = it * Q4_THREADS + tid;
+            bool on = i < total4;
+            int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (on && 4 * f < p.K) v = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
+            q4s_stage_one<SUBN>(v, on, m, f, sc, M, ncols, xs, cs, lane);
+        }
+    }
+    __syncthreads();
+    Q4S_TRACE(3)
+
+    // ---- stream this warp's run
+    const float fA = (SUBN ? 16777216.f : 1.f) * inv_sc;     // 2^24: undo the subnormal weight encoding
+    const float fB = (SUBN ? 1048576.f : 1.f) * inv_sc;      // 2^20: rows g+8 carry an extra factor 16
+    float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    const int gpr = p.nchunks / G;                            // groups per row pair-tile
+    int rp = gb / gpr;
+    int cg = gb - rp * gpr;                                   // group index inside the tile
+    const int first_rp = rp;
+    // per-lane pointers into the staged activation; lanes outside the real columns sit on a page of zeros
+    const bool bvalid = g < ncols, cvalid = SUBN && t < M;
+    const uint4* xs0 = bvalid ? xs + (g * 4 + t) * 2 : zero_pg;
+    const float4* cs0 = cvalid ? cs + t * 2 : reinterpret_cast<const float4*>(zero_pg);
+    const int xstep = bvalid ? ncols * 8 : 0;                 // uint4 per chunk
+    const int cstep = cvalid ? M * 2 : 0;                     // float4 per chunk
+    const uint4* xsp = xs0 + (size_t)cg * G * xstep;
+    const float4* csp = cs0 + (size_t)cg * G * cstep;
+    int s = 0;
+    uint32_t parity = 0;
+
+    // a tile wholly inside this warp's run goes straight to y; a tile it shares is parked in shared memory
+    auto flush = [&](int tile_rp) {
+        float v[4] = {acc[0][0] * fA, acc[0][1] * fB, acc[1][0] * fA, acc[1][1] * fB};
+        const int r0 = tile_rp * gpr;
+        if (gb <= r0 && r0 + gpr <= ge) {
+            q4s_store_tile(p, v, tile_rp, lane);
+        } else {
+            const int slot = tile_rp == first_rp ? 0 : 1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wpart[warp][slot][q][lane] = v[q];
+            if (lane == 0) wrp[warp][slot] = tile_rp;
+        }
+    };
+    bool timed_out = false;
+
+    for (int j = 0; j < ngroups; ++j) {
+        if (!mbar_wait(bars_u32 + s * 8, parity, Q4S_SPIN_LIMIT)) {
+            // record it, give the other copies in flight a short bounded chance to land, and leave
+            if (lane == 0) {
+                atomicExch(p.status, 1);
+                for (int o = 1; o < D; ++o) {
+                    int s2 = (s + o) % D;
+                    mbar_wait(bars_u32 + s2 * 8, s2 > s ? parity : parity ^ 1u, 1u << 12);
+                }
+            }
+            timed_out = true;
+            break;
+        }
+        const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)s * STAGE_BYTES);
+        if (!(p.dbg & 2)) {
+#pragma unroll
+            for (int q = 0; q < G; ++q) {
+                const uint4* un = st + q * Q4_UNIT_U4;
+                const uint4 w0 = un[lane], w1 = un[32 + lane], sv = un[64 + g];
+                const uint4 bf[2] = {xsp[0], xsp[1]};
+                const float4 cf[2] = {csp[0], csp[1]};
+                xsp += xstep;
+                csp += cstep;
+                const uint32_t wt[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
+                const uint32_t sw[2][2] = {{sv.x, sv.y}, {sv.z, sv.w}};
+#pragma unroll
+                for (int tile = 0; tile < 2; ++tile) {
+                    const float2 sA = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][0]));
+                    const float2 sB = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][1]));
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        uint32_t a0[4], a1[4];
+                        q4_unpack<SUBN>(wt[tile][2 * b], a0);
+                        q4_unpack<SUBN>(wt[tile][2 * b + 1], a1);
+                        float d[4];
+                        mma16816(d, a0, bf[b].x, bf[b].y, cf[b].x, cf[b].y, cf[b].z, cf[b].w);
+                        mma16816(d, a1, bf[b].z, bf[b].w, d[0], d[1], d[2], d[3]);
+                        acc[tile][0] = fmaf(b ? sA.y : sA.x, d[0] + d[1], acc[tile][0]);
+                        acc[tile][1] = fmaf(b ? sB.y : sB.x, d[2] + d[3], acc[tile][1]);
+                    }
+                }
+            }
+        } else {
+            xsp += G * xstep;
+            csp += G * cstep;
+        }
+        ++cg;
+        __syncwarp();
+        if (lane == 0 && issued < ngroups) {               // refill the stage just drained
+            mbar_expect_tx(bars_u32 + s * 8, STAGE_BYTES);
+            bulk_g2s(ring_u32 + s * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + s * 8);
+            gnext += STAGE_BYTES;
+            ++issued;
+        }
+        if (cg == gpr) {                                   // row pair-tile finished
+            if (!(p.dbg & 4)) flush(rp);
+            acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
+            cg = 0;
+            ++rp;
+            xsp = xs0;
+            csp = cs0;
+        }
+        if (++s == D) { s = 0; parity ^= 1u; }
+    }
+    Q4S_TRACE(4)
+    if (cg != 0 && !timed_out && !(p.dbg & 4)) flush(rp);  // the run ended inside a row pair-tile
+    __syncthreads();
+    Q4S_TRACE(5)
+
+    // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
+    // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
+    const int cta_gb = q4s_run_start(min(W, (int)blockIdx.x * Q4_WARPS), p.groups, W);
+    const int cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * Q4_WARPS), p.groups, W);
+    const int cta_first_rp = cta_gb / gpr;
+    for (int slot = 0; slot < 2; ++slot) {
+        const int my = wrp[warp][slot];
+        if (my < 0) continue;
+        int prev = -1;
+        for (int idx = warp * 2 + slot - 1; idx >= 0 && prev < 0; --idx) prev = wrp[idx >> 1][idx & 1];
+        if (prev == my) continue;                          // an earlier warp opened this tile
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] = wpart[warp][slot][q][lane];
+        for (int idx = warp * 2 + slot + 1; idx < Q4_WARPS * 2; ++idx) {
+            const int r = wrp[idx >> 1][idx & 1];
+            if (r < 0) continue;
+            if (r != my) break;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] += wpart[idx >> 1][idx & 1][q][lane];
+        }
+        const int r0 = my * gpr, r1 = r0 + gpr;
+        if (cta_gb <= r0 && r1 <= cta_ge) q4s_store_tile(p, v, my, lane);
+        else q4s_cross_cta(p, v, my, r0, r1, cta_first_rp, lane);
+    }
+    Q4S_TRACE(6)
 }
 
 }  // namespace mpq
