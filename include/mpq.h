@@ -95,7 +95,7 @@ int32_t mpq_q4_weight_create_dev(mpq_context* ctx, int64_t N, int64_t K,
 
 /* ---- NVFP4 weights ------------------------------------------------------- */
 /* B is given as [N][K/2] codes (K contiguous per output column) and [N][K/16]
- * e4m3 scales.  K must be a multiple of 128, N a multiple of 128. */
+ * e4m3 scales.  K must be a multiple of 32, N a multiple of 8. */
 int32_t mpq_nvfp4_weight_create(mpq_context* ctx, int64_t N, int64_t K,
                                 const uint8_t* codes_host, const uint8_t* sf_host,
                                 float tensor_scale, mpq_weight** out);
@@ -125,9 +125,9 @@ int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight* w, const 
 
 /* ---- NVFP4 GEMM ---------------------------------------------------------- */
 /* C[M][N] (bf16 bits, row-major) = bf16( tsA * tsB * sum_k A~[m,k] * B~[n,k] ).
- * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; M a
- * multiple of 128.  The activation scale factors are re-tiled on the GPU
- * inside this call (counted in its time). */
+ * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; any
+ * M >= 1.  The activation scale factors are re-tiled on the GPU inside this
+ * call (counted in its time) into scratch the context owns. */
 int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
                                const uint8_t* a_codes_dev, const uint8_t* a_sf_dev, float a_tensor_scale,
                                int64_t M, uint16_t* c_bf16_dev, void* stream);

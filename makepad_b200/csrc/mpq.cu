@@ -558,13 +558,17 @@ extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight
 extern "C" int32_t mpq_context_poll_status(mpq_context* ctx)
 {
     if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
-    if (!ctx->q4_status) return MPQ_OK;
     CU_TRY(ctx, cudaSetDevice(ctx->device));
-    int v = 0;
-    CU_TRY(ctx, cudaMemcpy(&v, ctx->q4_status, sizeof(int), cudaMemcpyDeviceToHost));   // synchronises with prior work
-    if (v == 0) return MPQ_OK;
-    cudaMemset(ctx->q4_status, 0, sizeof(int));         // a wait ran out: clear the word for the next launch
-    return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (code %d)", v);
+    int* words[2] = {ctx->q4_status, ctx->fp4.status};
+    for (int i = 0; i < 2; ++i) {
+        if (!words[i]) continue;
+        int v = 0;
+        CU_TRY(ctx, cudaMemcpy(&v, words[i], sizeof(int), cudaMemcpyDeviceToHost));    // synchronises with prior work
+        if (v == 0) continue;
+        cudaMemset(words[i], 0, sizeof(int));            // a wait ran out: clear the word for the next launch
+        return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (%s kernel, code %d)", i ? "NVFP4 GEMM" : "Q4", v);
+    }
+    return MPQ_OK;
 }
 
 // ---------------------------------------------------------------------------
@@ -576,8 +580,8 @@ extern "C" int32_t mpq_nvfp4_weight_create(mpq_context* ctx, int64_t N, int64_t 
     if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
     if (!out || !codes_host || !sf_host) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
     *out = nullptr;
-    if (N <= 0 || K <= 0 || N % 128 || K % 128)
-        return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 weight needs N and K positive multiples of 128 (N=%lld K=%lld)", (long long)N, (long long)K);
+    if (N <= 0 || K <= 0 || N % 8 || K % 32)
+        return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 weight needs N a positive multiple of 8 and K of 32 (N=%lld K=%lld)", (long long)N, (long long)K);
     if (N > (1LL << 30) || K > (1LL << 30)) return fail(ctx, MPQ_ERR_UNSUPPORTED, "dimension above 2^30");
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     mpq_weight* w = new (std::nothrow) mpq_weight();
@@ -606,7 +610,7 @@ extern "C" int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
     if (!w_ok(w) || !a_codes_dev || !a_sf_dev || !c_bf16_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale handle / pointer");
     if (w->fmt != MPQ_FMT_NVFP4) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight is not NVFP4");
     if (w->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight lives on device %d, context on %d", w->device, ctx->device);
-    if (M <= 0 || M % 128) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 GEMM needs M a positive multiple of 128 (M=%lld)", (long long)M);
+    if (M <= 0 || M > (1LL << 30)) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 GEMM needs 1 <= M <= 2^30 (M=%lld)", (long long)M);
     if (!aligned16(a_codes_dev) || !aligned16(a_sf_dev) || !aligned16(c_bf16_dev)) return fail(ctx, MPQ_ERR_ALIGN, "A, SFA and C must be 16-byte aligned");
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     std::string err;

@@ -30,7 +30,8 @@ struct Nvfp4Dev {
 struct Nvfp4Scratch {
     uint8_t* sfa_tiled = nullptr;      // activation scale factors re-tiled per call
     size_t sfa_bytes = 0;
-    void release() { cudaFree(sfa_tiled); sfa_tiled = nullptr; sfa_bytes = 0; }
+    int* status = nullptr;             // set non-zero when a bounded wait in the GEMM kernel ran out
+    void release() { cudaFree(sfa_tiled); cudaFree(status); sfa_tiled = nullptr; status = nullptr; sfa_bytes = 0; }
 };
 
 void nvfp4_dequant_launch(const uint8_t* codes, const uint8_t* sf, float ts, int64_t R, int64_t K, float* out, cudaStream_t s);

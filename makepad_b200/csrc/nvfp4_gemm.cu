@@ -1,8 +1,41 @@
-// NVFP4 block-scaled GEMM: weight build, scale-factor tiling, TMA + tcgen05 kernel.
+// NVFP4 block-scaled GEMM for sm_100a: weight build, scale-factor tiling, and a
+// persistent warp-specialised TMA + tcgen05 kernel with accumulators in TMEM.
+//
+//   C[M][N] (bf16) = tsA * tsB * sum_k A~[m,k] * B~[n,k]
+//   A~ = e2m1 code * e4m3 scale (one per 16 along K), likewise B~.
+//
+// No reference source exists for this path (the makepad/makepad snapshot has no
+// quantised-linear code); the operator is specified by the task configuration.
+//
+// TILE.  One CTA per SM loops over 128 x 224 output tiles (14336 = 64 * 224; two
+// fp32 accumulators of 224 columns plus the scale factors fit the 512 TMEM
+// columns, so the epilogue of one tile overlaps the MMAs of the next).  K is
+// consumed in blocks of 256 elements = 128 bytes per row = one 128-byte-swizzle
+// atom = four tcgen05.mma (K = 64 each).
+//
+// ROLES.  warp 0: TMA producer (A tile, B tile, the two scale-factor slabs).
+//         warp 1: TMEM allocation, tcgen05.cp of the scale factors, MMA issue.
+//         warps 2..5: epilogue (tcgen05.ld -> scale -> bf16 -> global).
+//
+// CODES need no repack: canonical [rows][K/2] bytes are K-major, which is what
+// the MMA's shared-memory descriptor (K-major, SWIZZLE_128B) wants; TMA applies
+// the swizzle.  SCALE FACTORS are re-tiled so that the 512 bytes one
+// tcgen05.cp.32x128b.warpx4 moves are contiguous: for 128 rows and one K step
+// of 64 (four scales per row), byte (row%32)*16 + (row/32)*4 + j.  A's slabs are
+// per 128 rows; B's are per 224-row output tile (two such atoms, the second
+// three-quarters full).
+//
+// No TMA load here uses cluster multicast.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
 #include "nvfp4.cuh"
 
 namespace mpq {
 
+// ---------------------------------------------------------------------------
+// exact export
+// ---------------------------------------------------------------------------
 __device__ __forceinline__ float e2m1_value(uint32_t nib)
 {
     // magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6}: exponent field e = (nib>>1)&3, mantissa bit m = nib&1
@@ -36,12 +69,74 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ codes, const ui
 }
 
 void nvfp4_dequant_launch(const uint8_t* codes, const uint8_t* sf, float ts, int64_t R, int64_t K, float* out,
-                                        cudaStream_t s)
+                          cudaStream_t s)
 {
     int64_t total = R * (K / 2);
     nvfp4_dequant_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(codes, sf, ts, R, K, out);
 }
 
+// ---------------------------------------------------------------------------
+// geometry
+// ---------------------------------------------------------------------------
+constexpr int BM = 128, BN = 224, BK = 256;               // BK in elements
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK / 2;                       // 16384
+constexpr int B_BYTES = BN * BK / 2;                       // 28672
+constexpr int SFA_BYTES = 4 * 512;                         // four K steps x one 128-row atom
+constexpr int SFB_BYTES = 4 * 2 * 512;                     // four K steps x two atoms (224 rows)
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 51200
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 512;
+constexpr int ACC_COL0 = 0, ACC_COL1 = BN, SFA_COL = 2 * BN, SFB_COL = 2 * BN + 16;   // 448, 464..495
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;     // polls of one mbarrier before the kernel gives up and reports it
+
+// scale factors of `rows` rows, tiled for tiles of `tile_rows` rows (128 for A, 224 for B):
+// dst[tile][kstep][atom][512] with atom = local_row / 128, zero where row or K step is out of range.
+// ksteps_pad = K steps of 64 rounded up to a multiple of 4 (one pipeline stage = four steps).
+__global__ void nvfp4_sf_tile_kernel(const uint8_t* __restrict__ sf, int64_t rows, int64_t K, int tile_rows, int atoms,
+                                     int ksteps_pad, int64_t total, uint8_t* __restrict__ dst)
+{
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per 4 bytes (one row, one K step)
+    if (i >= total) return;
+    int w = (int)(i & 127);                                          // word inside the 512-byte atom
+    int64_t rest = i >> 7;
+    int atom = (int)(rest % atoms);
+    rest /= atoms;
+    int kstep = (int)(rest % ksteps_pad);
+    int64_t tile = rest / ksteps_pad;
+    int r0 = w >> 2, r1 = w & 3;                                     // byte offset r0*16 + r1*4
+    int64_t local = (int64_t)atom * 128 + r1 * 32 + r0;
+    int64_t row = tile * tile_rows + local;
+    uint32_t v = 0;
+    if (local < tile_rows && row < rows && (int64_t)kstep * 64 < K) {
+        const uint8_t* src = sf + row * (K / 16) + (int64_t)kstep * 4;
+        int64_t nsf = K / 16 - (int64_t)kstep * 4;                   // K is a multiple of 16, maybe not of 64
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (j < nsf) v |= (uint32_t)src[j] << (8 * j);
+    }
+    reinterpret_cast<uint32_t*>(dst)[i] = v;
+}
+
+static inline int ksteps_padded(int64_t K) { return (int)(((K + 63) / 64 + 3) / 4 * 4); }
+
+static cudaError_t sf_tile_launch(const uint8_t* sf, int64_t rows, int64_t K, int tile_rows, uint8_t* dst, cudaStream_t s)
+{
+    int atoms = (tile_rows + 127) / 128;
+    int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+    int kp = ksteps_padded(K);
+    int64_t total = tiles * kp * atoms * 128;
+    nvfp4_sf_tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sf, rows, K, tile_rows, atoms, kp, total, dst);
+    return cudaGetLastError();
+}
+
+static size_t sf_tiled_bytes(int64_t rows, int64_t K, int tile_rows)
+{
+    int atoms = (tile_rows + 127) / 128;
+    int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+    return (size_t)tiles * ksteps_padded(K) * atoms * 512;
+}
 
 int32_t nvfp4_weight_build(Nvfp4Dev& w, int64_t N, int64_t K, const uint8_t* codes_host, const uint8_t* sf_host, float ts,
                            int* launches, std::string& err)
@@ -50,20 +145,342 @@ int32_t nvfp4_weight_build(Nvfp4Dev& w, int64_t N, int64_t K, const uint8_t* cod
     size_t cb = (size_t)N * (K / 2), sb = (size_t)N * (K / 16);
     cudaError_t e = cudaMalloc(&w.codes, cb);
     if (e == cudaSuccess) e = cudaMalloc(&w.sf_canonical, sb);
-    if (e == cudaSuccess) e = cudaMalloc(&w.sf_tiled, sb);
+    if (e == cudaSuccess) e = cudaMalloc(&w.sf_tiled, sf_tiled_bytes(N, K, BN));
     if (e == cudaSuccess) e = cudaMemcpy(w.codes, codes_host, cb, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(w.sf_canonical, sf_host, sb, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) { err = std::string("NVFP4 weight upload failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
-    *launches = 0;
+    if (e == cudaSuccess) e = sf_tile_launch(w.sf_canonical, N, K, BN, w.sf_tiled, 0);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    *launches = 1;
+    if (e != cudaSuccess) { err = std::string("NVFP4 weight build failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     return MPQ_OK;
 }
 
-int32_t nvfp4_gemm_launch(Nvfp4Scratch&, const Nvfp4Dev&, const uint8_t*, const uint8_t*, float, int64_t, uint16_t*, int,
-                          cudaStream_t, int* launches, std::string& err)
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t s2u(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait: false when the limit ran out
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "W_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra W_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 p, n, %3;\n\t"
+        "@p bra W_LOOP;\n\t"
+        "mov.u32 %0, 0;\n\t"
+        "bra W_END;\n\t"
+        "W_DONE:\n\t"
+        "mov.u32 %0, 1;\n\t"
+        "W_END:\n\t"
+        "}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(limit) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                            uint32_t sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+        "}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, SWIZZLE_128B: rows are 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);          // start address
+    d |= (uint64_t)1 << 16;                         // leading byte offset field (unused for swizzled K-major): 1
+    d |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                         // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+    return d;
+}
+// scale-factor atom: 32 rows of 16 bytes, no swizzle; 8-row core matrices 128 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(128 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+struct GemmParams {
+    const uint8_t* sfa;      // tiled
+    const uint8_t* sfb;      // tiled
+    __nv_bfloat16* C;
+    int M, N, K;
+    int m_tiles, n_tiles, k_blocks, ksteps_pad;
+    float scale;             // tsA * tsB
+    int* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile int s_abort;
+    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;          // SWIZZLE_128B tiles need 1024-byte alignment
+    const uint32_t bars = smem0 + STAGES * STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES, bar_acc_full = bars + 16 * STAGES,
+                   bar_acc_empty = bars + 16 * STAGES + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { bar_init(bar_acc_full + 8 * b, 1); bar_init(bar_acc_empty + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x) {
+                const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+                const uint8_t* sfa_t = p.sfa + (size_t)mt * p.ksteps_pad * 512;
+                const uint8_t* sfb_t = p.sfb + (size_t)nt * p.ksteps_pad * 1024;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bar_wait(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 3); s_abort = 1; break; }
+                    const uint32_t st = smem0 + stage * STAGE_BYTES, full = bar_full + 8 * stage;
+                    bar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(st, &map_a, kb * (BK / 2), mt * BM, full);
+                    tma_load_2d(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN, full);
+                    bulk_load(st + A_BYTES + B_BYTES, sfa_t + (size_t)kb * SFA_BYTES, SFA_BYTES, full);
+                    bulk_load(st + A_BYTES + B_BYTES + SFA_BYTES, sfb_t + (size_t)kb * SFB_BYTES, SFB_BYTES, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: A,B = e2m1 (1), K-major, N = BN, scale type ue4m3 (0), M = 128, K = 64 dense
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int stage = 0, abuf = 0, local = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x, ++local) {
+                abuf = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
+                if (!bar_wait(bar_acc_empty + 8 * abuf, aphase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 4); s_abort = 1; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (abuf ? ACC_COL1 : ACC_COL0);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bar_wait(bar_full + 8 * stage, phase, SPIN_LIMIT)) { atomicExch(p.status, 5); s_abort = 1; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem0 + stage * STAGE_BYTES;
+                    const uint32_t sfa_s = st + A_BYTES + B_BYTES, sfb_s = sfa_s + SFA_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        tc_cp_sf(tmem + SFA_COL + ks * 4, smem_desc_sf(sfa_s + ks * 512));
+                        tc_cp_sf(tmem + SFB_COL + ks * 8, smem_desc_sf(sfb_s + ks * 1024));
+                        tc_cp_sf(tmem + SFB_COL + ks * 8 + 4, smem_desc_sf(sfb_s + ks * 1024 + 512));
+                    }
+                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)        // +32 bytes along K inside the swizzle atom = +2 in the address field
+                        tc_mma_nvf4(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, tmem + SFA_COL + ks * 4, tmem + SFB_COL + ks * 8,
+                                    (kb | ks) ? 1u : 0u);
+                    tc_commit(bar_empty + 8 * stage);      // the stage may be refilled when these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                tc_commit(bar_acc_full + 8 * abuf);        // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x, ++local) {
+            const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            const int abuf = local & 1;
+            const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
+            if (!bar_wait(bar_acc_full + 8 * abuf, aphase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 6); s_abort = 1; } break; }
+            tc_fence_after();
+            const int row = mt * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (abuf ? ACC_COL1 : ACC_COL0);
+            __nv_bfloat16* crow = p.C + (size_t)row * p.N + (size_t)nt * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(taddr + c0, r);
+                tc_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
+                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        if (nt * BN + c0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = o;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar_acc_empty + 8 * abuf);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// rows x (K/2) bytes, K contiguous; box = box_rows x 128 bytes; 128-byte swizzle; out-of-range reads return zero
+static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_t* a_codes, const uint8_t* a_sf, float ta,
+                          int64_t M, uint16_t* c, int sm_count, cudaStream_t s, int* launches, std::string& err)
 {
     *launches = 0;
-    err = "NVFP4 GEMM kernel not built into this library";
-    return MPQ_ERR_UNSUPPORTED;
+    const int64_t N = w.N, K = w.K;
+    size_t need = sf_tiled_bytes(M, K, BM);
+    if (scratch.sfa_bytes < need) {
+        cudaDeviceSynchronize();
+        cudaFree(scratch.sfa_tiled);
+        scratch.sfa_tiled = nullptr;
+        scratch.sfa_bytes = 0;
+        cudaError_t e = cudaMalloc(&scratch.sfa_tiled, need);
+        if (e != cudaSuccess) { err = std::string("scratch allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+        scratch.sfa_bytes = need;
+    }
+    if (!scratch.status) {
+        cudaError_t e = cudaMalloc(&scratch.status, sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(scratch.status, 0, sizeof(int));
+        if (e != cudaSuccess) { err = std::string("status allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    }
+    cudaError_t e = sf_tile_launch(a_sf, M, K, BM, scratch.sfa_tiled, s);
+    *launches += 1;
+    if (e != cudaSuccess) { err = std::string("scale-factor tiling failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, a_codes, M, K, BM) || !make_map(&map_b, w.codes, N, K, BN)) {
+        err = "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, K a multiple of 32)";
+        return MPQ_ERR_CUDA;
+    }
+    GemmParams p;
+    p.sfa = scratch.sfa_tiled; p.sfb = w.sf_tiled; p.C = reinterpret_cast<__nv_bfloat16*>(c);
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.m_tiles = (int)((M + BM - 1) / BM); p.n_tiles = (int)((N + BN - 1) / BN);
+    p.k_blocks = (int)((K + BK - 1) / BK); p.ksteps_pad = ksteps_padded(K);
+    p.scale = ta * w.tensor_scale;
+    p.status = scratch.status;
+    static bool configured = false;
+    if (!configured) {
+        e = cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+        configured = true;
+    }
+    int grid = std::min(sm_count, p.m_tiles * p.n_tiles);
+    nvfp4_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+    *launches += 1;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { err = std::string("nvfp4_gemm_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    return MPQ_OK;
 }
 
 }  // namespace mpq
