@@ -123,6 +123,38 @@ int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float
 int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight* w, const float* x_host, int64_t M,
                                    float* y_host);
 
+/* ---- tensor parallelism --------------------------------------------------- */
+/* One process per GPU.  A COLUMN shard (mpq_q4_weight_create with MPQ_TP_COLUMN)
+ * needs no exchange: each rank's mpq_q4_linear_forward yields its slice of the
+ * output columns.  A ROW shard yields a partial output that must be summed
+ * over the ranks; the exchange below lets the kernel do that itself, through
+ * plain peer stores over NVLink, with no collective library in the data path.
+ *
+ * An exchange is a buffer on every rank that all ranks can write.  Create it
+ * on each rank, pass every rank's 64-byte IPC handle to every other rank (any
+ * host transport), and attach.  max_floats bounds M*N of the calls that use it.
+ * Single-process users holding peer-mapped pointers attach those directly. */
+int32_t mpq_exchange_create(mpq_context* ctx, int32_t rank, int32_t world, int64_t max_floats, mpq_exchange** out);
+int32_t mpq_exchange_ipc_handle(mpq_exchange* ex, uint8_t* out64);
+/* handles: world * 64 bytes, entry r = rank r's handle (the own entry is ignored). */
+int32_t mpq_exchange_attach(mpq_exchange* ex, const uint8_t* handles);
+/* buffers[r] = device pointer to rank r's exchange buffer as mapped in this process (own entry ignored). */
+int32_t mpq_exchange_attach_pointers(mpq_exchange* ex, void* const* buffers);
+int32_t mpq_exchange_buffer(mpq_exchange* ex, void** dev_ptr, int64_t* bytes);
+/* Polls a rank waits for one element of a peer's partial output before it gives up,
+ * records MPQ_ERR_PEER_TIMEOUT in the context's status word and returns (default 2^22). */
+int32_t mpq_exchange_set_wait_limit(mpq_exchange* ex, uint32_t polls);
+int32_t mpq_exchange_destroy(mpq_exchange* ex);
+/* Row-parallel linear with the sum over ranks fused into the kernel:
+ * Y[M][N] = sum_r X_r[M][K/world] . W_r^T on every rank.  Every rank must make the
+ * same sequence of calls on the exchange.  Consecutive calls alternate between the
+ * two halves of the buffer; a CUDA graph that is replayed must therefore contain an
+ * EVEN number of calls on one exchange.  After MPQ_ERR_PEER_TIMEOUT the exchange's
+ * contents are undefined: destroy it.  M <= 4 (MPQ_ERR_UNSUPPORTED otherwise: run
+ * mpq_q4_linear_forward and reduce with a collective library instead). */
+int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, mpq_exchange* ex,
+                                        const float* x_dev, int64_t M, float* y_dev, void* stream);
+
 /* ---- NVFP4 GEMM ---------------------------------------------------------- */
 /* C[M][N] (bf16 bits, row-major) = bf16( tsA * tsB * sum_k A~[m,k] * B~[n,k] ).
  * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; any

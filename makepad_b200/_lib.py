@@ -44,6 +44,14 @@ SIGNATURES = {
     "mpq_weight_destroy": (_i32, [_vp]),
     "mpq_q4_linear_forward": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "mpq_q4_linear_forward_host": (_i32, [_vp, _vp, _vp, _i64, _vp]),
+    "mpq_exchange_create": (_i32, [_vp, _i32, _i32, _i64, _pp]),
+    "mpq_exchange_ipc_handle": (_i32, [_vp, _vp]),
+    "mpq_exchange_attach": (_i32, [_vp, _vp]),
+    "mpq_exchange_attach_pointers": (_i32, [_vp, _pp]),
+    "mpq_exchange_buffer": (_i32, [_vp, _pp, C.POINTER(_i64)]),
+    "mpq_exchange_set_wait_limit": (_i32, [_vp, C.c_uint32]),
+    "mpq_exchange_destroy": (_i32, [_vp]),
+    "mpq_q4_linear_forward_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "mpq_nvfp4_gemm_forward": (_i32, [_vp, _vp, _vp, _vp, _f32, _i64, _vp, _vp]),
     "mpq_nvfp4_dequantize": (_i32, [_vp, _i64, _i64, _vp, _vp, _f32, _vp, _vp]),
 }

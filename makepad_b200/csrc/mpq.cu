@@ -53,7 +53,20 @@ struct mpq_weight {
 
 unsigned long long* g_trace = nullptr;
 extern "C" unsigned long long* mpq_debug_trace() { return g_trace; }
-static const uint32_t CTX_MAGIC = 0x4D505143u, W_MAGIC = 0x4D505157u;
+struct mpq_exchange {
+    uint32_t magic;
+    int device, rank, world;
+    int64_t max_floats;          // capacity of one slot, in values
+    uint2* local;                // [2 epoch halves][world slots][max_floats] (value, epoch) pairs
+    uint2* peer[8];              // every rank's buffer as mapped here (peer[rank] == local)
+    bool opened[8];              // mapped with cudaIpcOpenMemHandle (to be closed on destroy)
+    bool attached;
+    uint32_t epoch;
+    uint32_t wait_limit;
+};
+
+static const uint32_t CTX_MAGIC = 0x4D505143u, W_MAGIC = 0x4D505157u, X_MAGIC = 0x4D505158u;
+static bool x_ok(const mpq_exchange* x) { return x && x->magic == X_MAGIC; }
 
 static int32_t fail(mpq_context* ctx, int32_t code, const char* fmt, ...)
 {
@@ -371,7 +384,7 @@ static int32_t q4_stream_scratch(mpq_context* ctx, int warps)
         int n = std::max(warps, 4096);
         size_t bytes = (size_t)n * 2 * 32 * 4 * sizeof(uint2);
         CU_TRY(ctx, cudaMalloc(&ctx->q4_partials, bytes));
-        CU_TRY(ctx, cudaMemset(ctx->q4_partials, 0, bytes));      // tag 0 is never a launch's epoch
+        CU_TRY(ctx, cudaMemset(ctx->q4_partials, 0, bytes));      // tag 0 = empty slot
         ctx->q4_partials_warps = n;
     }
     return MPQ_OK;
@@ -435,23 +448,29 @@ static cudaError_t q4_stream_launch_nx(int nx, const Q4StreamLaunch& p, int grid
     }
 }
 
-// One launch for a slab of M <= 16 activation rows.
-static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
+// The streaming kernel for one slab of M <= 4 rows; with an exchange it also adds the ranks' partial outputs.
+static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4StreamPlan& pl, const float* x, int M, float* y,
+                                 int64_t ldy, mpq_exchange* ex, cudaStream_t s)
 {
-    Q4StreamPlan pl;
-    if (q4_stream_plan(ctx, q, M, &pl)) {
+    {
         const int sms = ctx->prop.multiProcessorCount;
         const int groups = (int)(q.units() / pl.G);
         int W = (int)std::min<int64_t>((int64_t)sms * Q4_WARPS * pl.ctas_per_sm, groups);
         W = std::min(W, Q4S_MAX_WARPS);
         int32_t st = q4_stream_scratch(ctx, W);
         if (st) return st;
-        if (++ctx->q4_epoch == 0) ctx->q4_epoch = 1;
         Q4StreamLaunch p;
         p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
         p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
-        p.partials = ctx->q4_partials; p.epoch = ctx->q4_epoch; p.status = ctx->q4_status;
+        p.partials = ctx->q4_partials; p.status = ctx->q4_status;
         { const char* d = getenv("MPQ_DBG"); p.dbg = d ? atoi(d) : 0; }
+        p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
+        for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
+        if (ex) {
+            const size_t half = (size_t)(++ex->epoch & 1u) * ex->world * ex->max_floats;
+            p.xworld = ex->world; p.xrank = ex->rank; p.xslot = ex->max_floats; p.xlimit = ex->wait_limit;
+            for (int r = 0; r < ex->world; ++r) p.xpeer[r] = ex->peer[r] + half;
+        }
         {
             static unsigned long long* trace = nullptr;
             static int trace_n = 0;
@@ -471,6 +490,13 @@ static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x,
         if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
         return MPQ_OK;
     }
+}
+
+// One launch for a slab of M <= 16 activation rows.
+static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
+{
+    Q4StreamPlan pl;
+    if (q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
     const int MT = M <= 4 ? 1 : (M <= 8 ? 2 : 4);
     const int sms = ctx->prop.multiProcessorCount;
     // K split across a thread-block cluster until the grid covers the machine about three times
@@ -555,6 +581,120 @@ extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight
     return MPQ_OK;
 }
 
+// ---------------------------------------------------------------------------
+// tensor-parallel exchange
+// ---------------------------------------------------------------------------
+extern "C" int32_t mpq_exchange_create(mpq_context* ctx, int32_t rank, int32_t world, int64_t max_floats, mpq_exchange** out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!out) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    *out = nullptr;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(ctx, MPQ_ERR_INVALID_ARG, "rank %d / world %d (world <= 8)", rank, world);
+    if (max_floats <= 0 || max_floats > (1LL << 26)) return fail(ctx, MPQ_ERR_SHAPE, "max_floats=%lld out of range", (long long)max_floats);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    mpq_exchange* x = new (std::nothrow) mpq_exchange();
+    if (!x) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
+    x->magic = X_MAGIC; x->device = ctx->device; x->rank = rank; x->world = world; x->max_floats = max_floats;
+    x->epoch = 0; x->wait_limit = 1u << 22; x->attached = world == 1;
+    for (int r = 0; r < 8; ++r) { x->peer[r] = nullptr; x->opened[r] = false; }
+    size_t bytes = (size_t)2 * world * max_floats * sizeof(uint2);
+    cudaError_t e = cudaMalloc(&x->local, bytes);
+    if (e == cudaSuccess) e = cudaMemset(x->local, 0, bytes);          // tag 0 = empty slot
+    if (e != cudaSuccess) {
+        cudaFree(x->local);
+        delete x;
+        return fail(ctx, MPQ_ERR_CUDA, "exchange allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    x->peer[rank] = x->local;
+    *out = x;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_ipc_handle(mpq_exchange* x, uint8_t* out64)
+{
+    if (!x_ok(x) || !out64) return MPQ_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    if (cudaSetDevice(x->device) != cudaSuccess || cudaIpcGetMemHandle(&h, x->local) != cudaSuccess) return MPQ_ERR_CUDA;
+    memcpy(out64, &h, 64);
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_attach(mpq_exchange* x, const uint8_t* handles)
+{
+    if (!x_ok(x) || !handles) return MPQ_ERR_INVALID_ARG;
+    if (x->attached) return MPQ_ERR_STATE;
+    if (cudaSetDevice(x->device) != cudaSuccess) return MPQ_ERR_CUDA;
+    for (int r = 0; r < x->world; ++r) {
+        if (r == x->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + 64 * r, 64);
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return MPQ_ERR_CUDA; }
+        x->peer[r] = reinterpret_cast<uint2*>(p);
+        x->opened[r] = true;
+    }
+    x->attached = true;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_attach_pointers(mpq_exchange* x, void* const* buffers)
+{
+    if (!x_ok(x) || !buffers) return MPQ_ERR_INVALID_ARG;
+    if (x->attached) return MPQ_ERR_STATE;
+    for (int r = 0; r < x->world; ++r) {
+        if (r == x->rank) continue;
+        if (!buffers[r]) return MPQ_ERR_INVALID_ARG;
+        x->peer[r] = reinterpret_cast<uint2*>(buffers[r]);
+    }
+    x->attached = true;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_buffer(mpq_exchange* x, void** dev_ptr, int64_t* bytes)
+{
+    if (!x_ok(x)) return MPQ_ERR_INVALID_ARG;
+    if (dev_ptr) *dev_ptr = x->local;
+    if (bytes) *bytes = (int64_t)2 * x->world * x->max_floats * (int64_t)sizeof(uint2);
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_set_wait_limit(mpq_exchange* x, uint32_t polls)
+{
+    if (!x_ok(x) || polls == 0) return MPQ_ERR_INVALID_ARG;
+    x->wait_limit = polls;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_destroy(mpq_exchange* x)
+{
+    if (!x_ok(x)) return MPQ_ERR_INVALID_ARG;
+    cudaSetDevice(x->device);
+    for (int r = 0; r < x->world; ++r)
+        if (x->opened[r]) cudaIpcCloseMemHandle(x->peer[r]);
+    cudaFree(x->local);
+    x->magic = 0;
+    delete x;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, mpq_exchange* ex, const float* x_dev,
+                                                   int64_t M, float* y_dev, void* stream)
+{
+    int32_t st = q4_validate(ctx, w, x_dev, M, y_dev);
+    if (st) return st;
+    if (!x_ok(ex)) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale exchange");
+    if (ex->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "exchange lives on device %d, context on %d", ex->device, ctx->device);
+    if (!ex->attached) return fail(ctx, MPQ_ERR_STATE, "exchange used before its peers were attached");
+    if (!aligned16(x_dev) || !aligned16(y_dev)) return fail(ctx, MPQ_ERR_ALIGN, "x and y must be 16-byte aligned");
+    if (M * w->q4.N > ex->max_floats) return fail(ctx, MPQ_ERR_UNSUPPORTED, "M*N=%lld exceeds the exchange capacity %lld", (long long)(M * w->q4.N), (long long)ex->max_floats);
+    Q4StreamPlan pl;
+    if (M > 4 || !q4_stream_plan(ctx, w->q4, (int)M, &pl))
+        return fail(ctx, MPQ_ERR_UNSUPPORTED, "the fused all-reduce needs M <= 4 and an activation that fits in shared memory");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    return q4_stream_forward(ctx, w->q4, pl, x_dev, (int)M, y_dev, w->q4.N, ex, (cudaStream_t)stream);
+}
+
 extern "C" int32_t mpq_context_poll_status(mpq_context* ctx)
 {
     if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
@@ -566,6 +706,8 @@ extern "C" int32_t mpq_context_poll_status(mpq_context* ctx)
         CU_TRY(ctx, cudaMemcpy(&v, words[i], sizeof(int), cudaMemcpyDeviceToHost));    // synchronises with prior work
         if (v == 0) continue;
         cudaMemset(words[i], 0, sizeof(int));            // a wait ran out: clear the word for the next launch
+        if (i == 0 && ctx->q4_partials)                  // ... and the slots the aborted launch may have left full
+            cudaMemset(ctx->q4_partials, 0, (size_t)ctx->q4_partials_warps * 2 * 32 * 4 * sizeof(uint2));
         return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (%s kernel, code %d)", i ? "NVFP4 GEMM" : "Q4", v);
     }
     return MPQ_OK;

@@ -458,8 +458,15 @@ struct Q4StreamLaunch {
     int warps_total;        // W: warps that own a run (<= 8*gridDim.x, <= groups)
     int depth;              // ring stages per warp
     uint2* partials;        // [CTAs][2][32 lanes][4] (value, epoch) pairs
-    uint32_t epoch;         // this launch's tag: differs from every earlier launch on the same scratch
     int* status;            // set non-zero when a bounded wait ran out
+    // row-parallel mode (xworld > 0): finished tiles are not written to Y but pushed, as (value, 1) pairs,
+    // into slot [xrank] of every rank's exchange buffer; then every rank adds the xworld slots of its own
+    // buffer, in rank order, into Y and clears them.  Consecutive launches alternate between the two
+    // halves of the buffer, so a fast rank cannot overwrite what a slow rank has not read yet.
+    int xworld, xrank;
+    uint2* xpeer[8];        // rank r's exchange buffer (this rank's own for r == xrank), already offset to this launch's half
+    int64_t xslot;          // uint2 per slot (>= M * N)
+    uint32_t xlimit;        // polls of one element before giving up
     int dbg;
     unsigned long long* trace;   // debug: [gridDim.x][8] timestamps of warp 0, or null
 };
@@ -526,6 +533,17 @@ __device__ __forceinline__ uint2 ld_tagged(const uint2* p)
 }
 
 // Write one finished row pair-tile to y.  v[tile*2+h] belongs to row tile*16 + g + 8h, activation row t.
+__device__ __forceinline__ void st_tagged_sys(uint2* p, float v, uint32_t tag)
+{
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged_sys(const uint2* p)
+{
+    uint2 r;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
+    return r;
+}
+
 __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const float (&v)[4], int rp, int lane)
 {
     const int g = lane >> 2, t = lane & 3;
@@ -533,16 +551,25 @@ __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const fl
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             int n = rp * 32 + (q >> 1) * 16 + g + 8 * (q & 1);
-            if (n < p.N) p.Y[(size_t)t * p.ldy + n] = v[q];
+            if (n < p.N) {
+                if (p.xworld > 0) {                      // plain peer stores over NVLink: one 8-byte store per rank
+                    const size_t e = (size_t)p.xrank * p.xslot + (size_t)t * p.N + n;
+                    for (int r = 0; r < p.xworld; ++r) st_tagged_sys(p.xpeer[r] + e, v[q], 1u);
+                } else {
+                    p.Y[(size_t)t * p.ldy + n] = v[q];
+                }
+            }
         }
     }
 }
 
 // A row pair-tile cut by the boundary between two CTAs' runs.  Every CTA but the first that shares
-// the tile stores its partial as (value, epoch) pairs -- one aligned 8-byte store each, so a reader
-// that sees the epoch sees the value, with no fence and no counter -- and carries on.  The first CTA,
-// for which the tile is the END of its run, polls the others' slots (bounded), adds them in CTA
-// order, so the sum does not depend on timing, and writes y.
+// the tile stores its partial as (value, 1) pairs -- one aligned 8-byte store each, so a reader that
+// sees the tag sees the value, with no fence and no counter -- and carries on.  The first CTA, for
+// which the tile is the END of its run, polls the others' slots (bounded), adds them in CTA order, so
+// the sum does not depend on timing, writes y, and clears the slots it consumed.  A slot is written
+// once and read once per launch, and the next launch writes only after this one has completed, so the
+// protocol needs no per-launch state (it is safe under CUDA-graph replay).
 __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4], int rp, int r0, int r1, int cta_first_rp,
                                            int lane)
 {
@@ -551,7 +578,7 @@ __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4
     if ((int)blockIdx.x != c0) {
         uint2* mine = p.partials + (((size_t)blockIdx.x * 2 + (rp == cta_first_rp ? 0 : 1)) * 32 + lane) * 4;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], p.epoch);
+        for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], 1u);
         return;
     }
     const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4_WARPS;
@@ -566,8 +593,8 @@ __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4
             for (int u = 0; u < 4; ++u)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    r[u][q] = (c + u <= c1) ? ld_tagged(src + (size_t)u * 256 + q) : make_uint2(0u, p.epoch);
-                    ok = ok && (r[u][q].y == p.epoch);
+                    r[u][q] = (c + u <= c1) ? ld_tagged(src + (size_t)u * 256 + q) : make_uint2(0u, 1u);
+                    ok = ok && (r[u][q].y == 1u);
                 }
             ok = __all_sync(0xFFFFFFFFu, ok);
         }
@@ -578,7 +605,10 @@ __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll
-            for (int q = 0; q < 4; ++q) v[q] += __uint_as_float(r[u][q].x);
+            for (int q = 0; q < 4; ++q) {
+                v[q] += __uint_as_float(r[u][q].x);
+                if (c + u <= c1) st_tagged(const_cast<uint2*>(src) + (size_t)u * 256 + q, 0.f, 0u);   // consumed: free the slot
+            }
         src += 4 * 256;
     }
     q4s_store_tile(p, v, rp, lane);
@@ -883,6 +913,31 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
         else q4s_cross_cta(p, v, my, r0, r1, cta_first_rp, lane);
     }
     Q4S_TRACE(6)
+
+    // ---- row-parallel: add the ranks' partial outputs.  The tagged pairs need no flag and no grid
+    // barrier: an element is ready when all xworld copies of it carry the tag.
+    if (p.xworld > 0) {
+        const uint2* mine = p.xpeer[p.xrank];
+        const int total = p.M * p.N;
+        for (int e = blockIdx.x * Q4_THREADS + tid; e < total; e += gridDim.x * Q4_THREADS) {
+            float sum = 0.f;
+            bool ok = true;
+            for (int r = 0; r < p.xworld && ok; ++r) {
+                const uint2* src = mine + (size_t)r * p.xslot + e;
+                uint2 v = ld_tagged_sys(src);
+                for (uint32_t spin = 0; v.y != 1u && spin < p.xlimit; ++spin) {
+                    __nanosleep(64);
+                    v = ld_tagged_sys(src);
+                }
+                ok = v.y == 1u;
+                sum += __uint_as_float(v.x);
+                if (ok) st_tagged_sys(const_cast<uint2*>(src), 0.f, 0u);      // consumed: free the slot
+            }
+            if (!ok) { atomicExch(p.status, 7); break; }       // a peer never delivered: report it and leave
+            const int m = e / p.N;
+            p.Y[(size_t)m * p.ldy + (e - m * p.N)] = sum;
+        }
+    }
 }
 
 }  // namespace mpq
