@@ -118,6 +118,25 @@ int32_t mpq_weight_destroy(mpq_weight* w);
  * of two); a non-finite x yields non-finite outputs in its row. */
 int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
                               float* y_dev, void* stream);
+/* Same result as mpq_q4_linear_forward for callers that must not let the
+ * library allocate (no counterpart in the reference; added for hosts that run
+ * inside a fixed memory budget or on a thread that may not enter the CUDA
+ * allocator): this call and everything under it performs no cudaMalloc,
+ * cudaFree or other allocating routine.  The scratch the M <= 4 kernel needs
+ * -- slots for output tiles shared between CTAs -- is a 1 MiB static device
+ * array inside the library (512 CTAs' worth; every GPU that loads the library
+ * holds it until exit).  A launch that would need more slots is rejected with
+ * MPQ_ERR_UNSUPPORTED.  All calls on one device share that array: they must be
+ * ordered on the GPU (calls that overlap there race on the slots).  The slots
+ * are empty again after every completed call, so nothing needs clearing
+ * between calls.  If a bounded wait ran out (status_dev non-zero), slots may be
+ * left full: do not use this entry point again on that device in this process.
+ * The first call on a device looks up the array's device
+ * address and raises the kernels' shared-memory limit; make that call before
+ * any stream capture.  status_dev, if not NULL, is a caller-owned device int
+ * that a kernel sets non-zero when one of its bounded waits runs out. */
+int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
+                                     float* y_dev, int32_t* status_dev, void* stream);
 /* Convenience end-to-end call with HOST buffers: copies X up, runs, copies Y
  * back and synchronises. */
 int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight* w, const float* x_host, int64_t M,

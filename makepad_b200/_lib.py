@@ -43,6 +43,7 @@ SIGNATURES = {
     "mpq_weight_device_bytes": (_i64, [_vp]),
     "mpq_weight_destroy": (_i32, [_vp]),
     "mpq_q4_linear_forward": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
+    "mpq_q4_linear_forward_static": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp]),
     "mpq_q4_linear_forward_host": (_i32, [_vp, _vp, _vp, _i64, _vp]),
     "mpq_exchange_create": (_i32, [_vp, _i32, _i32, _i64, _pp]),
     "mpq_exchange_ipc_handle": (_i32, [_vp, _vp]),

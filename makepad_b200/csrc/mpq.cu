@@ -493,10 +493,17 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
 }
 
 // One launch for a slab of M <= 16 activation rows.
+static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s);
 static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
 {
     Q4StreamPlan pl;
     if (q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
+    return q4_forward_general(ctx, q, x, M, y, ldy, s);
+}
+
+// The phase-staged kernel: any M <= 16, any K; needs no scratch memory.
+static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
+{
     const int MT = M <= 4 ? 1 : (M <= 8 ? 2 : 4);
     const int sms = ctx->prop.multiProcessorCount;
     // K split across a thread-block cluster until the grid covers the machine about three times
@@ -578,6 +585,72 @@ extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight
     if ((st = q4_forward_checked(ctx, w, ctx->hx, M, ctx->hy, w->q4.N, 0))) return st;
     CU_TRY(ctx, cudaMemcpyAsync(y_host, ctx->hy, yb, cudaMemcpyDeviceToHost, 0));
     CU_TRY(ctx, cudaStreamSynchronize(0));
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Q4 linear without any allocation
+// ---------------------------------------------------------------------------
+// Some callers cannot let the library allocate: a host thread that replays work inside a fixed memory
+// budget, a real-time loop that must not enter the allocator's locks, code that runs while another
+// thread holds the device in a state where cudaMalloc would synchronise.  mpq_q4_linear_forward
+// allocates lazily (the streaming kernel's scratch, on a context's first call); this variant never
+// does.  Its scratch is the array below, which every GPU that loads the library holds until exit.
+constexpr int Q4_STATIC_MAX_CTAS = 512;                                   // two CTAs per SM on up to 256 SMs
+constexpr size_t Q4_STATIC_SLOT_BYTES = (size_t)Q4_STATIC_MAX_CTAS * 2 * 32 * 4 * sizeof(uint2);   // 1 MiB
+static __device__ __align__(256) unsigned char g_q4_static_scratch[256 + Q4_STATIC_SLOT_BYTES];
+// In host code the array's name is only a stand-in: the device address comes from cudaGetSymbolAddress,
+// once per device, with that device current.
+static unsigned char* g_q4_static_ptr[64] = {};
+
+extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
+                                                float* y_dev, int32_t* status_dev, void* stream)
+{
+    int32_t st = q4_validate(ctx, w, x_dev, M, y_dev);
+    if (st) return st;
+    if (!aligned16(x_dev) || !aligned16(y_dev)) return fail(ctx, MPQ_ERR_ALIGN, "x and y must be 16-byte aligned");
+    if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, MPQ_ERR_UNSUPPORTED, "device index %d beyond the static table", ctx->device);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    if (!g_q4_static_ptr[ctx->device]) {                  // set-up: the first call on this device
+        void* p = nullptr;
+        CU_TRY(ctx, cudaGetSymbolAddress(&p, g_q4_static_scratch));
+        g_q4_static_ptr[ctx->device] = static_cast<unsigned char*>(p);
+    }
+    unsigned char* base = g_q4_static_ptr[ctx->device];
+    const Q4Dev& q = w->q4;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int64_t m0 = 0; m0 < M; m0 += 16) {
+        const int m = (int)std::min<int64_t>(16, M - m0);
+        const float* x = x_dev + (size_t)m0 * q.K;
+        float* y = y_dev + (size_t)m0 * q.N;
+        Q4StreamPlan pl;
+        if (!q4_stream_plan(ctx, q, m, &pl)) {            // the phase-staged kernel uses no scratch at all
+            st = q4_forward_general(ctx, q, x, m, y, q.N, s);
+            if (st) return st;
+            continue;
+        }
+        const int sms = ctx->prop.multiProcessorCount;
+        const int groups = (int)(q.units() / pl.G);
+        const int W = (int)std::min<int64_t>((int64_t)sms * Q4_WARPS * pl.ctas_per_sm, groups);
+        const int grid = (W + Q4_WARPS - 1) / Q4_WARPS;
+        if (grid > Q4_STATIC_MAX_CTAS)
+            return fail(ctx, MPQ_ERR_UNSUPPORTED, "this launch needs %d scratch slots, the static array holds %d", grid, Q4_STATIC_MAX_CTAS);
+        Q4StreamLaunch p;
+        p.stream = q.stream; p.X = x; p.Y = y; p.M = m; p.N = (int)q.N; p.K = (int)q.K; p.ldy = q.N;
+        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
+        p.partials = reinterpret_cast<uint2*>(base + 256);
+        p.status = status_dev ? status_dev : reinterpret_cast<int*>(base);
+        p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
+        for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
+        p.dbg = 0;
+        p.trace = nullptr;
+        cudaError_t e;
+        const bool subn = ctx->q4_variant == 0;
+        if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
+        else e = subn ? q4_stream_launch_nx<true, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
+        ctx->launches += 1;
+        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
+    }
     return MPQ_OK;
 }
 

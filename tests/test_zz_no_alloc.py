@@ -1,0 +1,50 @@
+"""The allocation-free Q4 entry point, for hosts that must not let the library allocate (a fixed memory
+budget, a thread that may not enter the CUDA allocator): its scratch is a static device array inside the
+library.  Called through the C ABI twice in a row, it must give exactly what the ordinary entry point
+gives.  This file is collected last, so a run that stops at the first failure has run everything else.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from makepad_b200 import _lib, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
+    import torch
+    import makepad_b200
+    ctx = makepad_b200.Context(0)           # a fresh context: the ordinary path's scratch is not even allocated yet
+    lib = ctx.lib
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for (N, K) in [(4096, 4096), (1000, 2048), (4096, 11008)]:       # tiles shared between CTAs in all of them
+        codes, scales = synth.q4_weight(N, K, seed=31)
+        w = makepad_b200.Q4Weight(ctx, codes, scales)
+        for M in (1, 3, 4, 7, 20):                                   # M > 4 takes the scratch-free kernel, M > 16 two slabs
+            x = torch.from_numpy(synth.activations(M, K, seed=32)).cuda()
+            outs = []
+            for _ in range(2):                                       # two calls in a row share the static array
+                y = torch.full((M, N), float("nan"), device="cuda")
+                ctx.check(lib.mpq_q4_linear_forward_static(ctx.h, w.h, C.c_void_p(x.data_ptr()), M, C.c_void_p(y.data_ptr()),
+                                                           C.c_void_p(status.data_ptr()), s))
+                outs.append(y)
+            want = torch.empty((M, N), device="cuda")
+            ctx.check(lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(x.data_ptr()), M, C.c_void_p(want.data_ptr()), s))
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+            ref = orc.q4_matmul_f64(codes, scales, x.cpu().numpy())
+            assert orc.rel_err(want.cpu().numpy(), ref)[1] < 1e-3
+        w.destroy()
+    # NULL status pointer is accepted; bad arguments are rejected like the ordinary entry point's
+    codes, scales = synth.q4_weight(64, 128, seed=33)
+    w = makepad_b200.Q4Weight(ctx, codes, scales)
+    x = torch.zeros(128, device="cuda"); y = torch.zeros(64, device="cuda")
+    assert lib.mpq_q4_linear_forward_static(ctx.h, w.h, C.c_void_p(x.data_ptr()), 1, C.c_void_p(y.data_ptr()), None, s) == _lib.OK
+    assert lib.mpq_q4_linear_forward_static(ctx.h, w.h, C.c_void_p(x.data_ptr() + 4), 1, C.c_void_p(y.data_ptr()), None, s) == _lib.ERR_ALIGN
+    assert lib.mpq_q4_linear_forward_static(ctx.h, w.h, None, 1, C.c_void_p(y.data_ptr()), None, s) == _lib.ERR_INVALID_ARG
+    torch.cuda.synchronize()
+    ctx.close()
