@@ -39,7 +39,9 @@ struct mpq_context {
     int* q4_status;
     bool q4_stream;           // use the streaming kernel where the activation fits in shared memory
     int q4_group;             // chunks per bulk copy of the streaming kernel (2 or 4)
-    int q4_ctas;              // CTAs per SM the streaming kernel aims for
+    int q4_ctas;              // (unused by the one-CTA-per-SM streaming kernel; kept for experiments)
+    bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
+    int q4_depth;             // most ring stages per warp
     Nvfp4Scratch fp4;
 };
 
@@ -139,9 +141,13 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     e = getenv("MPQ_Q4_STREAM");
     c->q4_stream = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_GROUP");
-    c->q4_group = (e && e[0] == '2') ? 2 : 4;
+    c->q4_group = (e && e[0] == '4') ? 4 : 2;
     e = getenv("MPQ_Q4_CTAS");
     c->q4_ctas = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    e = getenv("MPQ_Q4_DEPTH");
+    c->q4_depth = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    e = getenv("MPQ_Q4_TILE");
+    c->q4_tile_mode = !(e && e[0] == '0');
     *out = c;
     return MPQ_OK;
 }
@@ -395,20 +401,20 @@ struct Q4StreamPlan { int depth, G, nx, ctas_per_sm; size_t smem; };
 static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4StreamPlan* pl)
 {
     if (!ctx->q4_stream || M > 4) return false;
-    const int G = ctx->q4_group;
     size_t nblk = (size_t)q.nchunks * 2;
-    size_t xbytes = nblk * (2 * M) * 64 + nblk * M * 16 + 8 * 8 * Q4_WARPS;
-    size_t stage = (size_t)Q4_WARPS * G * Q4_UNIT_BYTES;
-    int need = (M * q.nchunks + 15) / 16;                 // float4 of x per thread
-    pl->G = G;
-    pl->nx = need <= 4 ? 4 : need <= 12 ? 12 : need <= 28 ? 28 : 0;
-    const int max_ctas = pl->nx == 28 ? 1 : ctx->q4_ctas;
-    // deepest ring that still lets max_ctas CTAs share an SM; else fewer CTAs
-    for (int ctas = max_ctas; ctas >= 1; --ctas) {
-        size_t budget = (size_t)(227 * 1024) / ctas - 10 * 1024;      // static shared memory (8.2 KiB) + 1 KiB the system reserves per CTA
-        for (int d = 4; d >= 2; --d) {
+    size_t xbytes = nblk * (2 * M) * 64 + nblk * M * 16 + 8 * 8 * Q4S_WARPS;
+    int need = (M * q.nchunks + 31) / 32;                 // float4 of x per thread (512 threads)
+    pl->nx = need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 0;
+    pl->ctas_per_sm = 1;
+    // one CTA per SM: 227 KiB less the kernel's static shared memory (17 KiB) and the 1 KiB the system reserves
+    const size_t budget = (size_t)(227 - 18) * 1024;
+    const int prefer = ctx->q4_group;
+    for (int pass = 0; pass < 2; ++pass) {
+        const int G = pass == 0 ? prefer : (prefer == 4 ? 2 : 4);
+        const size_t stage = (size_t)Q4S_WARPS * G * Q4_UNIT_BYTES;
+        for (int d = std::min(ctx->q4_depth, G == 4 ? 2 : 4); d >= 1; --d) {
             size_t total = stage * d + xbytes;
-            if (total <= budget && (ctas > 1 || d >= 2)) { pl->depth = d; pl->smem = total; pl->ctas_per_sm = ctas; return true; }
+            if (total <= budget) { pl->G = G; pl->depth = d; pl->smem = total; return true; }
         }
     }
     return false;
@@ -420,13 +426,13 @@ static cudaError_t q4_stream_launch_t(const Q4StreamLaunch& p, int grid, size_t 
     auto kern = q4_stream_kernel<SUBN, G, NX, MINB>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(217 * 1024));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(209 * 1024));
         if (e != cudaSuccess) return e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(Q4_THREADS);
+    cfg.blockDim = dim3(Q4S_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -441,10 +447,10 @@ template <bool SUBN, int G>
 static cudaError_t q4_stream_launch_nx(int nx, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
 {
     switch (nx) {
-        case 4: return q4_stream_launch_t<SUBN, G, 4, 2>(p, grid, smem, pdl, s);
-        case 12: return q4_stream_launch_t<SUBN, G, 12, 2>(p, grid, smem, pdl, s);
-        case 28: return q4_stream_launch_t<SUBN, G, 28, 1>(p, grid, smem, pdl, s);
-        default: return q4_stream_launch_t<SUBN, G, 0, 2>(p, grid, smem, pdl, s);
+        case 4: return q4_stream_launch_t<SUBN, G, 4, 1>(p, grid, smem, pdl, s);
+        case 8: return q4_stream_launch_t<SUBN, G, 8, 1>(p, grid, smem, pdl, s);
+        case 16: return q4_stream_launch_t<SUBN, G, 16, 1>(p, grid, smem, pdl, s);
+        default: return q4_stream_launch_t<SUBN, G, 0, 1>(p, grid, smem, pdl, s);
     }
 }
 
@@ -455,11 +461,14 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
     {
         const int sms = ctx->prop.multiProcessorCount;
         const int groups = (int)(q.units() / pl.G);
-        int W = (int)std::min<int64_t>((int64_t)sms * Q4_WARPS * pl.ctas_per_sm, groups);
+        int W = (int)std::min<int64_t>((int64_t)sms * Q4S_WARPS, groups);
         W = std::min(W, Q4S_MAX_WARPS);
         int32_t st = q4_stream_scratch(ctx, W);
         if (st) return st;
         Q4StreamLaunch p;
+        // whole row pair-tiles per CTA when there is about one per SM or more: no tile is then shared between CTAs
+        p.tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
+        p.nrp = q.nrp;
         p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
         p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
         p.partials = ctx->q4_partials; p.status = ctx->q4_status;
@@ -481,7 +490,7 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
                 g_trace = trace;
             }
         }
-        int grid = (W + Q4_WARPS - 1) / Q4_WARPS;
+        int grid = p.tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
         cudaError_t e;
         const bool subn = ctx->q4_variant == 0;
         if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
@@ -631,13 +640,15 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
         }
         const int sms = ctx->prop.multiProcessorCount;
         const int groups = (int)(q.units() / pl.G);
-        const int W = (int)std::min<int64_t>((int64_t)sms * Q4_WARPS * pl.ctas_per_sm, groups);
-        const int grid = (W + Q4_WARPS - 1) / Q4_WARPS;
+        const int W = (int)std::min<int64_t>((int64_t)sms * Q4S_WARPS, groups);
+        const int tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
+        const int grid = tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
         if (grid > Q4_STATIC_MAX_CTAS)
             return fail(ctx, MPQ_ERR_UNSUPPORTED, "this launch needs %d scratch slots, the static array holds %d", grid, Q4_STATIC_MAX_CTAS);
         Q4StreamLaunch p;
         p.stream = q.stream; p.X = x; p.Y = y; p.M = m; p.N = (int)q.N; p.K = (int)q.K; p.ldy = q.N;
         p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
+        p.tile_mode = tile_mode; p.nrp = q.nrp;
         p.partials = reinterpret_cast<uint2*>(base + 256);
         p.status = status_dev ? status_dev : reinterpret_cast<int*>(base);
         p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;

@@ -432,10 +432,14 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // ---------------------------------------------------------------------------
 // the streaming kernel: M <= 4, whole x resident in shared memory
 // ---------------------------------------------------------------------------
-// Eight warps per CTA, no CTA-wide synchronisation after the activation has been
-// staged.  The unit stream is cut into W equal contiguous runs of GROUPS (G
-// consecutive chunks of one row pair-tile; the layout pads K so that a group
-// never straddles a tile), one run per warp.  Each warp owns a private ring of
+// One CTA of sixteen warps per SM, no CTA-wide synchronisation between staging
+// the activation and draining the runs.  The unit stream is cut into contiguous
+// runs of GROUPS (G consecutive chunks of one row pair-tile; the layout pads K
+// so that a group never straddles a tile), one run per warp.  When the matrix
+// has at least about one row pair-tile per SM, each CTA takes WHOLE tiles and
+// its warps split them, so no tile is shared between CTAs; otherwise (few
+// rows, e.g. a tensor-parallel shard) all warps of the grid take equal runs and
+// tiles cut by a CTA boundary are finished through global scratch.  Each warp owns a private ring of
 // shared-memory stages that its lane 0 keeps full with cp.async.bulk copies
 // (mbarrier complete_tx), so the HBM stream of a warp never waits for its
 // arithmetic and -- because the first copies are issued BEFORE
@@ -444,6 +448,8 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // to y.  A tile shared by warps of one CTA is summed through shared memory, in
 // warp order, when the CTA has drained its runs.  A tile cut by the boundary
 // between two CTAs is finished through global scratch (q4s_cross_cta).
+constexpr int Q4S_WARPS = 16;                   // one CTA of sixteen warps per SM
+constexpr int Q4S_THREADS = Q4S_WARPS * 32;
 constexpr int Q4_GROUP_PAD = 4;                  // chunks per row pair-tile are padded to a multiple of this
 constexpr uint32_t Q4S_SPIN_LIMIT = 1u << 22;    // polls of one mbarrier before giving up
 
@@ -455,7 +461,9 @@ struct Q4StreamLaunch {
     int64_t ldy;
     int nchunks;            // per row pair-tile, a multiple of G
     int groups;             // nrp * nchunks / G
-    int warps_total;        // W: warps that own a run (<= 8*gridDim.x, <= groups)
+    int warps_total;        // W: warps that own a run (<= 16*gridDim.x, <= groups); split mode only
+    int tile_mode;          // 1: CTA b owns row pair-tiles [b*nrp/grid, (b+1)*nrp/grid) and its warps split them
+    int nrp;                // row pair-tiles
     int depth;              // ring stages per warp
     uint2* partials;        // [CTAs][2][32 lanes][4] (value, epoch) pairs
     int* status;            // set non-zero when a bounded wait ran out
@@ -505,10 +513,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
         : "=r"(ok) : "r"(bar), "r"(parity), "r"(limit) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+// Weights are read once per call: the copies carry an evict-first L2 policy so that they do not push the
+// (small, re-read) activations and outputs out of L2.
+__device__ __forceinline__ uint64_t l2_evict_first_policy()
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
 
 __device__ __forceinline__ int q4s_run_start(int i, int groups, int W) { return (int)(((int64_t)i * groups) / W); }
@@ -570,18 +586,19 @@ __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const fl
 // the sum does not depend on timing, writes y, and clears the slots it consumed.  A slot is written
 // once and read once per launch, and the next launch writes only after this one has completed, so the
 // protocol needs no per-launch state (it is safe under CUDA-graph replay).
-__device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float (&v)[4], int rp, int r0, int r1, int cta_first_rp,
-                                           int lane)
+__device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float v0, float v1, float v2, float v3, int rp, int r0,
+                                           int r1, int cta_first_rp, int lane)
 {
+    float v[4] = {v0, v1, v2, v3};
     const int W = p.warps_total;
-    const int c0 = q4s_owner(r0, p.groups, W) / Q4_WARPS;
+    const int c0 = q4s_owner(r0, p.groups, W) / Q4S_WARPS;
     if ((int)blockIdx.x != c0) {
         uint2* mine = p.partials + (((size_t)blockIdx.x * 2 + (rp == cta_first_rp ? 0 : 1)) * 32 + lane) * 4;
 #pragma unroll
         for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], 1u);
         return;
     }
-    const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4_WARPS;
+    const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4S_WARPS;
     // every later CTA starts its run inside this tile, so the tile is its first one (slot 0)
     const uint2* src = p.partials + (((size_t)(c0 + 1) * 2) * 32 + lane) * 4;
     for (int c = c0 + 1; c <= c1; c += 4) {                // four contributors' loads in flight at a time
@@ -662,13 +679,13 @@ __device__ __forceinline__ void q4s_stage_one(float4 v, bool on, int m, int f, f
 // NX = float4 of x each thread keeps in registers between the max pass and the conversion pass
 //      (0: re-read x from global memory instead, for activations too long for the register file).
 template <bool SUBN, int G, int NX, int MINB>
-__global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4StreamLaunch p)
+__global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4StreamLaunch p)
 {
     constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ uint32_t s_max[Q4_WARPS];
-    __shared__ float wpart[Q4_WARPS][2][4][32];   // each warp's partial first / last tile, [q][lane]
-    __shared__ int wrp[Q4_WARPS][2];              // the tile index of each, -1 if none
+    __shared__ uint32_t s_max[Q4S_WARPS];
+    __shared__ float wpart[Q4S_WARPS][2][4][32];   // each warp's partial first / last tile, [q][lane]
+    __shared__ int wrp[Q4S_WARPS][2];              // the tile index of each, -1 if none
     __shared__ uint4 zero_pg[2];                  // what lanes outside the 2M real columns read
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -683,15 +700,25 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     }
     Q4S_TRACE(0)
     unsigned char* ring = smem_raw + (size_t)warp * D * STAGE_BYTES;
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)Q4_WARPS * D * STAGE_BYTES);
+    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)Q4S_WARPS * D * STAGE_BYTES);
     float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nblk * ncols * 64);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)nblk * M * 16) + warp * 8;
 
     const int W = p.warps_total;
-    const int gw = blockIdx.x * Q4_WARPS + warp;
-    const bool active = gw < W;
-    const int gb = active ? q4s_run_start(gw, p.groups, W) : 0;
-    const int ge = active ? q4s_run_start(gw + 1, p.groups, W) : 0;
+    const int gw = blockIdx.x * Q4S_WARPS + warp;
+    const int gpr = p.nchunks / G;                            // groups per row pair-tile
+    int cta_gb, cta_ge, gb, ge;
+    if (p.tile_mode) {
+        cta_gb = (int)(((int64_t)blockIdx.x * p.nrp) / gridDim.x) * gpr;
+        cta_ge = (int)(((int64_t)(blockIdx.x + 1) * p.nrp) / gridDim.x) * gpr;
+        gb = cta_gb + (int)(((int64_t)warp * (cta_ge - cta_gb)) / Q4S_WARPS);
+        ge = cta_gb + (int)(((int64_t)(warp + 1) * (cta_ge - cta_gb)) / Q4S_WARPS);
+    } else {
+        cta_gb = q4s_run_start(min(W, (int)blockIdx.x * Q4S_WARPS), p.groups, W);
+        cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * Q4S_WARPS), p.groups, W);
+        gb = gw < W ? q4s_run_start(gw, p.groups, W) : 0;
+        ge = gw < W ? q4s_run_start(gw + 1, p.groups, W) : 0;
+    }
     const int ngroups = ge - gb;
     const unsigned char* gnext = reinterpret_cast<const unsigned char*>(p.stream) + (size_t)gb * STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring), bars_u32 = smem_u32(bars);
@@ -702,11 +729,12 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     }
     __syncwarp();
     int issued = 0;
+    const uint64_t l2pol = l2_evict_first_policy();
     if (lane == 0) {
         const int first = min(D, ngroups);
         for (; issued < first; ++issued) {
             mbar_expect_tx(bars_u32 + issued * 8, STAGE_BYTES);
-            bulk_g2s(ring_u32 + issued * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + issued * 8);
+            bulk_g2s(ring_u32 + issued * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + issued * 8, l2pol);
             gnext += STAGE_BYTES;
         }
     }
@@ -724,7 +752,7 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     if (NX > 0) {
 #pragma unroll
         for (int it = 0; it < NX; ++it) {
-            int i = it * Q4_THREADS + tid;
+            int i = it * Q4S_THREADS + tid;
             int m = i / pk4, f = i - m * pk4;
             xv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (i < total4 && 4 * f < p.K) xv[it] = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
@@ -737,7 +765,7 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
             mx = max(mx, __float_as_uint(xv[it].w) & 0x7FFFFFFFu);
         }
     } else {
-        for (int i = tid; i < total4; i += Q4_THREADS) {
+        for (int i = tid; i < total4; i += Q4S_THREADS) {
             int m = i / pk4, f = i - m * pk4;
             if (4 * f < p.K) {
                 float4 v = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
@@ -754,7 +782,7 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     __syncthreads();
     mx = s_max[0];
 #pragma unroll
-    for (int w = 1; w < Q4_WARPS; ++w) mx = max(mx, s_max[w]);
+    for (int w = 1; w < Q4S_WARPS; ++w) mx = max(mx, s_max[w]);
     int emax = (int)(mx >> 23);
     float sc = 1.f, inv_sc = 1.f;
     if (mx != 0 && emax < 255) {
@@ -765,15 +793,15 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     if (NX > 0) {
 #pragma unroll
         for (int it = 0; it < NX; ++it) {
-            int i = it * Q4_THREADS + tid;
+            int i = it * Q4S_THREADS + tid;
             bool on = i < total4;
             int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
             q4s_stage_one<SUBN>(xv[it], on, m, f, sc, M, ncols, xs, cs, lane);
         }
     } else {
-        const int iters = (total4 + Q4_THREADS - 1) / Q4_THREADS;
+        const int iters = (total4 + Q4S_THREADS - 1) / Q4S_THREADS;
         for (int it = 0; it < iters; ++it) {
-            int i = it * Q4_THREADS + tid;
+            int i = it * Q4S_THREADS + tid;
             bool on = i < total4;
             int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -788,7 +816,6 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     const float fA = (SUBN ? 16777216.f : 1.f) * inv_sc;     // 2^24: undo the subnormal weight encoding
     const float fB = (SUBN ? 1048576.f : 1.f) * inv_sc;      // 2^20: rows g+8 carry an extra factor 16
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-    const int gpr = p.nchunks / G;                            // groups per row pair-tile
     int rp = gb / gpr;
     int cg = gb - rp * gpr;                                   // group index inside the tile
     const int first_rp = rp;
@@ -868,7 +895,7 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
         __syncwarp();
         if (lane == 0 && issued < ngroups) {               // refill the stage just drained
             mbar_expect_tx(bars_u32 + s * 8, STAGE_BYTES);
-            bulk_g2s(ring_u32 + s * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + s * 8);
+            bulk_g2s(ring_u32 + s * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + s * 8, l2pol);
             gnext += STAGE_BYTES;
             ++issued;
         }
@@ -889,28 +916,28 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
 
     // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
     // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
-    const int cta_gb = q4s_run_start(min(W, (int)blockIdx.x * Q4_WARPS), p.groups, W);
-    const int cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * Q4_WARPS), p.groups, W);
     const int cta_first_rp = cta_gb / gpr;
+    const int entry = wrp[lane >> 1][lane & 1];             // lane i holds segment i = (warp i/2, slot i%2)
+#pragma unroll
     for (int slot = 0; slot < 2; ++slot) {
-        const int my = wrp[warp][slot];
+        const int idx0 = warp * 2 + slot;
+        const int my = __shfl_sync(0xFFFFFFFFu, entry, idx0);
         if (my < 0) continue;
-        int prev = -1;
-        for (int idx = warp * 2 + slot - 1; idx >= 0 && prev < 0; --idx) prev = wrp[idx >> 1][idx & 1];
-        if (prev == my) continue;                          // an earlier warp opened this tile
-        float v[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = wpart[warp][slot][q][lane];
-        for (int idx = warp * 2 + slot + 1; idx < Q4_WARPS * 2; ++idx) {
-            const int r = wrp[idx >> 1][idx & 1];
-            if (r < 0) continue;
-            if (r != my) break;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) v[q] += wpart[idx >> 1][idx & 1][q][lane];
+        uint32_t same = __ballot_sync(0xFFFFFFFFu, entry == my);
+        if (same & ((1u << idx0) - 1u)) continue;           // an earlier warp opened this tile
+        float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+        for (; same; same &= same - 1u) {                   // ascending segment order: a fixed summation order
+            const int idx = __ffs(same) - 1;
+            const float* src = &wpart[idx >> 1][idx & 1][0][lane];
+            v0 += src[0]; v1 += src[32]; v2 += src[64]; v3 += src[96];
         }
         const int r0 = my * gpr, r1 = r0 + gpr;
-        if (cta_gb <= r0 && r1 <= cta_ge) q4s_store_tile(p, v, my, lane);
-        else q4s_cross_cta(p, v, my, r0, r1, cta_first_rp, lane);
+        if (cta_gb <= r0 && r1 <= cta_ge) {
+            const float v[4] = {v0, v1, v2, v3};
+            q4s_store_tile(p, v, my, lane);
+        } else {
+            q4s_cross_cta(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
+        }
     }
     Q4S_TRACE(6)
 
@@ -919,7 +946,7 @@ __global__ void __launch_bounds__(Q4_THREADS, MINB) q4_stream_kernel(const Q4Str
     if (p.xworld > 0) {
         const uint2* mine = p.xpeer[p.xrank];
         const int total = p.M * p.N;
-        for (int e = blockIdx.x * Q4_THREADS + tid; e < total; e += gridDim.x * Q4_THREADS) {
+        for (int e = blockIdx.x * Q4S_THREADS + tid; e < total; e += gridDim.x * Q4S_THREADS) {
             float sum = 0.f;
             bool ok = true;
             for (int r = 0; r < p.xworld && ok; ++r) {
