@@ -114,6 +114,108 @@ def cpu_arm(steps: int, warmup: int, threads: int):
     return 1.0 / (32 * dt), dt
 
 
+def _time_graph(torch, enqueue, stream, reps):
+    """Median-free simple timing: capture `enqueue` as a graph, replay `reps` times between CUDA events (us per replay)."""
+    with torch.cuda.stream(stream):
+        enqueue(); enqueue()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        enqueue()
+    g.replay(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def extras(ctx, peak):
+    """The other configurations of the task, measured in the same run (N = 1): single Q4 matvec (config 0),
+    small-M verify batches (config 2), NVFP4 prefill GEMM (config 3), the 70B-shape FFN on one GPU (config 4)."""
+    import ctypes as C
+    import torch
+    import makepad_b200
+    from makepad_b200.decode_stack import DecodeStack, SHAPES_70B_FFN, q4_bytes, random_q4_weight_on_device
+    out = {}
+    side = torch.cuda.Stream()
+    # config 0: 4096 x 4096, M = 1; 43 distinct copies so that every launch misses L2
+    ws = [random_q4_weight_on_device(ctx, 4096, 4096, 1000 + i) for i in range(43)]
+    x = torch.randn(1, 4096, device="cuda"); y = torch.empty(1, 4096, device="cuda")
+    def enq():
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for w in ws:
+            ctx.check(ctx.lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(x.data_ptr()), 1, C.c_void_p(y.data_ptr()), s))
+    us = _time_graph(torch, enq, side, 10) / len(ws)
+    b = q4_bytes(4096, 4096, 1)
+    out["q4_matvec_4096x4096_m1"] = {"us": us, "gbs": b / us / 1e3, "frac_of_hbm_peak": b / us / 1e3 / peak}
+    for w in ws:
+        w.destroy()
+    # config 2: small-M verify batches on the 7B shapes (4 layers of distinct weights = 455 MB > L2)
+    small = {}
+    for M in (1, 2, 4, 8, 16):
+        st = DecodeStack(ctx, layers=4, M=M, seed=7).capture()
+        for _ in range(3):
+            st.step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(st.stream):
+            e0.record()
+            for _ in range(20):
+                st.step()
+            e1.record()
+        torch.cuda.synchronize()
+        us_layer = e0.elapsed_time(e1) * 1e3 / 20 / 4
+        small[f"M={M}"] = {"us_per_layer": us_layer, "gbs": st.bytes_per_step / 4 / us_layer / 1e3}
+        st.destroy()
+    for k in small:
+        small[k]["time_vs_m1"] = small[k]["us_per_layer"] / small["M=1"]["us_per_layer"]
+    out["q4_small_m_7b_layer"] = small
+    # config 4 on one GPU: 70B-shape FFN, M = 1 (two copies of each weight: 793 MB per pass)
+    st = DecodeStack(ctx, layers=2, M=1, shapes=SHAPES_70B_FFN, seed=9).capture()
+    for _ in range(3):
+        st.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st.stream):
+        e0.record()
+        for _ in range(20):
+            st.step()
+        e1.record()
+    torch.cuda.synchronize()
+    us_ffn = e0.elapsed_time(e1) * 1e3 / 20 / 2
+    out["q4_70b_ffn_m1"] = {"us_per_ffn": us_ffn, "gbs": st.bytes_per_step / 2 / us_ffn / 1e3, "frac_of_hbm_peak": st.bytes_per_step / 2 / us_ffn / 1e3 / peak}
+    st.destroy()
+    # config 3: NVFP4 prefill GEMM 2048 x 4096 x 14336 -> bf16, L2 flushed between launches
+    M, N, K = 2048, 14336, 4096
+    g = torch.Generator(device="cuda"); g.manual_seed(3)
+    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    bq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    sfa = torch.randint(0x10, 0x40, (M, K // 16), dtype=torch.uint8, device="cuda", generator=g)
+    sfb = torch.randint(0x10, 0x40, (N, K // 16), dtype=torch.uint8, device="cuda", generator=g)
+    w = makepad_b200.Nvfp4Weight(ctx, bq.cpu().numpy(), sfb.cpu().numpy(), 1.0)
+    lin = makepad_b200.QuantLinear(w)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):
+        lin((a, sfa, 1.0), out=c)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ts = []
+    for _ in range(15):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); lin((a, sfa, 1.0), out=c); e1.record(); torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    us = ts[len(ts) // 2]
+    out["nvfp4_gemm_2048x4096x14336"] = {"us": us, "tflops": 2.0 * M * N * K / us / 1e6, "frac_of_nominal_dense_fp4_9pf": 2.0 * M * N * K / us / 1e6 / 9000.0,
+                                         "note": "includes re-tiling the activation scale factors; L2 flushed between launches"}
+    w.destroy()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -121,6 +223,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="mpq", choices=["mpq", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=20)
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations (config 0, 2, 3, 4 on one GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -225,6 +328,12 @@ def main():
         "gpu_launches": launches * args.steps,
         "clocks": clocks,
     }
+    if world == 1 and not args.no_extra:
+        stack.destroy()
+        del stack
+        torch.cuda.empty_cache()
+        out["extra"] = extras(ctx, peak)
+        ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
     if world == 1:
         toks_cpu, dt = cpu_arm(args.cpu_steps, 2, threads)
         out["cpu_baseline"] = {"value": toks_cpu, "unit": "tokens/s", "cores": threads, "kind": "port",

@@ -42,6 +42,7 @@ struct mpq_context {
     int q4_ctas;              // (unused by the one-CTA-per-SM streaming kernel; kept for experiments)
     bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
     int q4_depth;             // most ring stages per warp
+    bool q4_slab4;            // M > 4 as slabs of four rows through the streaming kernel
     Nvfp4Scratch fp4;
 };
 
@@ -146,6 +147,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_ctas = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_DEPTH");
     c->q4_depth = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    e = getenv("MPQ_Q4_SLAB4");
+    c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
     c->q4_tile_mode = !(e && e[0] == '0');
     *out = c;
@@ -539,11 +542,29 @@ static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float*
     return MPQ_OK;
 }
 
+// Rows per launch for M activation rows: the streaming kernel's widest slab (4, 2 or 1 rows) whose staged
+// activation fits in shared memory, else 16 through the phase-staged kernel.
+static int q4_slab_rows(const mpq_context* ctx, const Q4Dev& q, int64_t M)
+{
+    Q4StreamPlan pl;
+    if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) return (int)M;      // one launch of the streaming kernel
+    if (ctx->q4_slab4 && M > 1) {
+        const int widths[3] = {4, 2, 1};
+        for (int i = 0; i < 3; ++i)
+            if (widths[i] < M && q4_stream_plan(ctx, q, widths[i], &pl)) return widths[i];
+    }
+    return 16;
+}
+
 static int32_t q4_forward_checked(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M, float* y_dev,
                                   int64_t ldy, cudaStream_t s)
 {
-    for (int64_t m0 = 0; m0 < M; m0 += 16) {
-        int m = (int)std::min<int64_t>(16, M - m0);
+    // M > 4: slabs of four rows through the streaming kernel where it applies (it re-reads the weights per
+    // slab but runs near the HBM roofline), else slabs of sixteen through the phase-staged kernel, whose
+    // legacy-MMA arithmetic is the bound from M = 8 up.
+    const int slab = q4_slab_rows(ctx, w->q4, M);
+    for (int64_t m0 = 0; m0 < M; m0 += slab) {
+        int m = (int)std::min<int64_t>(slab, M - m0);
         int32_t st = q4_forward_slab(ctx, w->q4, x_dev + (size_t)m0 * w->q4.K, m, y_dev + (size_t)m0 * ldy, ldy, s);
         if (st) return st;
     }
@@ -628,8 +649,9 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
     unsigned char* base = g_q4_static_ptr[ctx->device];
     const Q4Dev& q = w->q4;
     cudaStream_t s = (cudaStream_t)stream;
-    for (int64_t m0 = 0; m0 < M; m0 += 16) {
-        const int m = (int)std::min<int64_t>(16, M - m0);
+    const int slab = q4_slab_rows(ctx, q, M);          // the same split into launches as mpq_q4_linear_forward
+    for (int64_t m0 = 0; m0 < M; m0 += slab) {
+        const int m = (int)std::min<int64_t>(slab, M - m0);
         const float* x = x_dev + (size_t)m0 * q.K;
         float* y = y_dev + (size_t)m0 * q.N;
         Q4StreamPlan pl;

@@ -184,7 +184,7 @@ def test_host_buffer_entry_point(ctx, orc):
 
 
 def test_general_kernel_covers_small_m_too(orc):
-    """With the streaming kernel switched off, M <= 4 runs through the phase-staged kernel."""
+    """With the streaming kernel switched off, every M runs through the phase-staged kernel (all three MMA tile counts)."""
     import makepad_b200
     os.environ["MPQ_Q4_STREAM"] = "0"
     try:
@@ -194,7 +194,7 @@ def test_general_kernel_covers_small_m_too(orc):
     for (N, K) in [(40, 160), (512, 4096), (4096, 11008)]:
         codes, scales = synth.q4_weight(N, K, seed=1)
         w = makepad_b200.Q4Weight(c2, codes, scales)
-        for M in (1, 3, 4):
+        for M in (1, 3, 4, 7, 16):
             x = synth.activations(M, K, seed=2)
             got = _forward(c2, w, x)
             assert orc.rel_err(got, orc.q4_matmul_f64(codes, scales, x))[1] < TOL

@@ -23,7 +23,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
     for (N, K) in [(4096, 4096), (1000, 2048), (4096, 11008)]:       # tiles shared between CTAs in all of them
         codes, scales = synth.q4_weight(N, K, seed=31)
         w = makepad_b200.Q4Weight(ctx, codes, scales)
-        for M in (1, 3, 4, 7, 20):                                   # M > 4 takes the scratch-free kernel, M > 16 two slabs
+        for M in (1, 3, 4, 7, 20):                                   # M > 4 runs as several launches
             x = torch.from_numpy(synth.activations(M, K, seed=32)).cuda()
             outs = []
             for _ in range(2):                                       # two calls in a row share the static array
