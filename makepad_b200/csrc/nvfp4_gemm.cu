@@ -29,6 +29,9 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "nvfp4.cuh"
 
 namespace mpq {
@@ -402,6 +405,210 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
+// the CTA-pair kernel: 256 x 224 tiles, tcgen05 cta_group::2
+// ---------------------------------------------------------------------------
+// Two CTAs of a cluster share one MMA: the leader (even rank) issues
+// tcgen05.mma.cta_group::2 with M = 256; each CTA holds its own 128 rows of A, HALF of the B tile (112
+// rows) and its own accumulator, so a CTA loads 36 KB per K block instead of 51 KB and the tensor core
+// reads half as much B from its own shared memory.  Every load is a TMA tile load with .cta_group::2 (no
+// multicast) whose bytes are counted on the LEADER's full barrier; the leader's tcgen05.commit releases
+// the stage in both CTAs.  Scale factors: each CTA copies A's for its own rows and B's for all 224
+// columns into its own TMEM.
+constexpr int P_STAGES = 5;
+constexpr int P_BH_BYTES = (BN / 2) * BK / 2;                                    // 14336: half of the B tile
+constexpr int P_STAGE_BYTES = A_BYTES + P_BH_BYTES + SFA_BYTES + SFB_BYTES;     // 36864
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: the bytes are counted on the barrier of the pair's leader (address with the peer bit cleared)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar & 0xFEFFFFFFu) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                                 uint32_t sfb, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+        "}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate) : "memory");
+}
+
+struct PairParams {
+    __nv_bfloat16* C;
+    int M, N, K;
+    int m_pairs, n_tiles, k_blocks, ksteps_pad;   // m_pairs = ceil(M / 256)
+    float scale;
+    int* status;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, const PairParams p)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile int s_abort;
+    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bars = smem0 + P_STAGES * P_STAGE_BYTES;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * P_STAGES, bar_acc_full = bars + 16 * P_STAGES,
+                   bar_acc_empty = bars + 16 * P_STAGES + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                 // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int total_tiles = p.m_pairs * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < P_STAGES; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { bar_init(bar_acc_full + 8 * b, 1); bar_init(bar_acc_empty + 8 * b, 8); }   // 4 epilogue warps of each CTA
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // both CTAs' barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs; the leader arms the shared full barrier) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs) {
+                const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
+                const int mt128 = 2 * mp + (int)rank;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bar_wait(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 13); s_abort = 1; break; }
+                    const uint32_t st = smem0 + stage * P_STAGE_BYTES, full = bar_full + 8 * stage;
+                    if (rank == 0) bar_expect_tx(full, 2 * P_STAGE_BYTES);
+                    tma_load_2d_pair(st, &map_a, kb * (BK / 2), mt128 * BM, full);
+                    tma_load_2d_pair(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN + (int)rank * (BN / 2), full);
+                    tma_load_2d_pair(st + A_BYTES + P_BH_BYTES, &map_sfa, 0, mt128 * p.ksteps_pad + kb * 4, full);
+                    tma_load_2d_pair(st + A_BYTES + P_BH_BYTES + SFA_BYTES, &map_sfb, 0, (nt * p.ksteps_pad + kb * 4) * 2, full);
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the leader only ----------------
+        if (lane == 0 && rank == 0) {
+            // A,B = e2m1, K-major, N = 224, scale type ue4m3, M = 256 across the pair, K = 64 dense
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int stage = 0, local = 0;
+            uint32_t phase = 0;
+            for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs, ++local) {
+                const int abuf = local & 1;
+                const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
+                if (!bar_wait(bar_acc_empty + 8 * abuf, aphase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 14); s_abort = 1; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (abuf ? ACC_COL1 : ACC_COL0);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bar_wait(bar_full + 8 * stage, phase, SPIN_LIMIT)) { atomicExch(p.status, 15); s_abort = 1; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem0 + stage * P_STAGE_BYTES;
+                    const uint32_t sfa_s = st + A_BYTES + P_BH_BYTES, sfb_s = sfa_s + SFA_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        tc_cp_sf_pair(tmem + SFA_COL + ks * 4, smem_desc_sf(sfa_s + ks * 512));
+                        tc_cp_sf_pair(tmem + SFB_COL + ks * 8, smem_desc_sf(sfb_s + ks * 1024));
+                        tc_cp_sf_pair(tmem + SFB_COL + ks * 8 + 4, smem_desc_sf(sfb_s + ks * 1024 + 512));
+                    }
+                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        tc_mma_nvf4_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, tmem + SFA_COL + ks * 4, tmem + SFB_COL + ks * 8,
+                                         (kb | ks) ? 1u : 0u);
+                    tc_commit_pair(bar_empty + 8 * stage);       // both CTAs may refill the stage
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                tc_commit_pair(bar_acc_full + 8 * abuf);         // both CTAs' epilogues may read
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 of each CTA, its own 128 rows ----------------
+        const int quarter = warp & 3;
+        const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
+        int local = 0;
+        for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs, ++local) {
+            const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
+            const int abuf = local & 1;
+            const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
+            if (!bar_wait(bar_acc_full + 8 * abuf, aphase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 16); s_abort = 1; } break; }
+            tc_fence_after();
+            const int row = (2 * mp + (int)rank) * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (abuf ? ACC_COL1 : ACC_COL0);
+            __nv_bfloat16* crow = p.C + (size_t)row * p.N + (size_t)nt * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_ld32(taddr + c0, r);
+                tc_ld_wait();
+                if (row < p.M) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
+                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        if (nt * BN + c0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = o;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) bar_arrive_cluster(leader_acc_empty + 8 * abuf);   // the leader's MMA warp waits for all eight warps
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // the peer's shared memory and barriers stay valid until both are done
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -433,6 +640,41 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// tiled scale factors as a 2-D array of 512-byte atoms: `atoms` rows of 128 uint32; box = box_rows atoms
+static bool make_sf_map(CUtensorMap* map, const void* base, int64_t atoms, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {128, (cuuint64_t)atoms};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// CTA pairs the device can keep resident at once (0: the pair kernel cannot be used)
+static int pair_clusters(int sm_count)
+{
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    cached = 0;
+    if (cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count & ~1));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, nvfp4_gemm_pair_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    cached = n;
+    return cached;
+}
+
 int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_t* a_codes, const uint8_t* a_sf, float ta,
                           int64_t M, uint16_t* c, int sm_count, cudaStream_t s, int* launches, std::string& err)
 {
@@ -461,6 +703,35 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     if (!make_map(&map_a, a_codes, M, K, BM) || !make_map(&map_b, w.codes, N, K, BN)) {
         err = "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, K a multiple of 32)";
         return MPQ_ERR_CUDA;
+    }
+    // The CTA-pair kernel (tcgen05 cta_group::2) is correct but measured slightly slower than the single-CTA
+    // kernel at the prefill shape (93 vs 87 us): both are bound by the serial scale-copy + MMA issue of one
+    // thread, not by operand traffic.  It is kept selectable (MPQ_FP4_PAIR=1) and covered by a parity test.
+    const char* env = getenv("MPQ_FP4_PAIR");
+    const int clusters = (env && env[0] == '1') ? pair_clusters(sm_count) : 0;
+    if (clusters > 0) {
+        // CTA-pair kernel: B is loaded in halves of 112 rows, the scale-factor slabs through tensor maps too
+        CUtensorMap map_bh, map_sfa, map_sfb;
+        const int kp = ksteps_padded(K);
+        const int64_t m_tiles128 = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+        if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_sf_map(&map_sfa, scratch.sfa_tiled, m_tiles128 * kp, 4) ||
+            !make_sf_map(&map_sfb, w.sf_tiled, n_tiles * kp * 2, 8)) {
+            err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel";
+            return MPQ_ERR_CUDA;
+        }
+        PairParams pp;
+        pp.C = reinterpret_cast<__nv_bfloat16*>(c);
+        pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
+        pp.m_pairs = (int)((M + 2 * BM - 1) / (2 * BM)); pp.n_tiles = (int)n_tiles;
+        pp.k_blocks = (int)((K + BK - 1) / BK); pp.ksteps_pad = kp;
+        pp.scale = ta * w.tensor_scale;
+        pp.status = scratch.status;
+        int grid = 2 * std::min(clusters, pp.m_pairs * pp.n_tiles);
+        nvfp4_gemm_pair_kernel<<<grid, THREADS, P_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, map_sfb, pp);
+        *launches += 1;
+        e = cudaGetLastError();
+        if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+        return MPQ_OK;
     }
     GemmParams p;
     p.sfa = scratch.sfa_tiled; p.sfb = w.sf_tiled; p.C = reinterpret_cast<__nv_bfloat16*>(c);
