@@ -31,15 +31,13 @@ struct mpq_context {
     // staging for the *_host convenience calls (grown on demand)
     float *hx, *hy;
     size_t hx_bytes, hy_bytes;
-    // scratch of the streaming Q4 kernel: epoch-tagged partial tiles of row pair-tiles cut by a run
-    // boundary (two slots per warp), the epoch of the last launch, one status word
+    // scratch of the streaming Q4 kernel: tagged partial tiles of row pair-tiles cut by a boundary
+    // between two CTAs' runs (two slots per CTA; write-once / read-once per launch), one status word
     uint2* q4_partials;
     int q4_partials_warps;
-    uint32_t q4_epoch;
     int* q4_status;
     bool q4_stream;           // use the streaming kernel where the activation fits in shared memory
     int q4_group;             // chunks per bulk copy of the streaming kernel (2 or 4)
-    int q4_ctas;              // (unused by the one-CTA-per-SM streaming kernel; kept for experiments)
     bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
     int q4_depth;             // most ring stages per warp
     bool q4_slab4;            // M > 4 as slabs of four rows through the streaming kernel
@@ -54,17 +52,15 @@ struct mpq_weight {
     Nvfp4Dev fp4;
 };
 
-unsigned long long* g_trace = nullptr;
-extern "C" unsigned long long* mpq_debug_trace() { return g_trace; }
 struct mpq_exchange {
     uint32_t magic;
     int device, rank, world;
     int64_t max_floats;          // capacity of one slot, in values
-    uint2* local;                // [2 epoch halves][world slots][max_floats] (value, epoch) pairs
+    uint2* local;                // [2 halves][world slots][max_floats] (value, tag) pairs
     uint2* peer[8];              // every rank's buffer as mapped here (peer[rank] == local)
     bool opened[8];              // mapped with cudaIpcOpenMemHandle (to be closed on destroy)
     bool attached;
-    uint32_t epoch;
+    uint32_t calls;              // launches so far: its parity picks the half of the buffer
     uint32_t wait_limit;
 };
 
@@ -125,7 +121,6 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->hx_bytes = c->hy_bytes = 0;
     c->q4_partials = nullptr;
     c->q4_partials_warps = 0;
-    c->q4_epoch = 0;
     c->q4_status = nullptr;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&c->prop, device) != cudaSuccess) {
         delete c;
@@ -143,8 +138,6 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_stream = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_GROUP");
     c->q4_group = (e && e[0] == '4') ? 4 : 2;
-    e = getenv("MPQ_Q4_CTAS");
-    c->q4_ctas = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_DEPTH");
     c->q4_depth = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_SLAB4");
@@ -475,23 +468,12 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
         p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
         p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
         p.partials = ctx->q4_partials; p.status = ctx->q4_status;
-        { const char* d = getenv("MPQ_DBG"); p.dbg = d ? atoi(d) : 0; }
         p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
         for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
         if (ex) {
-            const size_t half = (size_t)(++ex->epoch & 1u) * ex->world * ex->max_floats;
+            const size_t half = (size_t)(++ex->calls & 1u) * ex->world * ex->max_floats;
             p.xworld = ex->world; p.xrank = ex->rank; p.xslot = ex->max_floats; p.xlimit = ex->wait_limit;
             for (int r = 0; r < ex->world; ++r) p.xpeer[r] = ex->peer[r] + half;
-        }
-        {
-            static unsigned long long* trace = nullptr;
-            static int trace_n = 0;
-            p.trace = nullptr;
-            if (getenv("MPQ_TRACE")) {
-                if (!trace) cudaMallocManaged(&trace, (size_t)64 * 1024 * 8 * 8);
-                p.trace = trace + (size_t)(trace_n++ % 64) * 1024 * 8;
-                g_trace = trace;
-            }
         }
         int grid = p.tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
         cudaError_t e;
@@ -675,8 +657,6 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
         p.status = status_dev ? status_dev : reinterpret_cast<int*>(base);
         p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
         for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
-        p.dbg = 0;
-        p.trace = nullptr;
         cudaError_t e;
         const bool subn = ctx->q4_variant == 0;
         if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
@@ -701,7 +681,7 @@ extern "C" int32_t mpq_exchange_create(mpq_context* ctx, int32_t rank, int32_t w
     mpq_exchange* x = new (std::nothrow) mpq_exchange();
     if (!x) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
     x->magic = X_MAGIC; x->device = ctx->device; x->rank = rank; x->world = world; x->max_floats = max_floats;
-    x->epoch = 0; x->wait_limit = 1u << 22; x->attached = world == 1;
+    x->calls = 0; x->wait_limit = 1u << 22; x->attached = world == 1;
     for (int r = 0; r < 8; ++r) { x->peer[r] = nullptr; x->opened[r] = false; }
     size_t bytes = (size_t)2 * world * max_floats * sizeof(uint2);
     cudaError_t e = cudaMalloc(&x->local, bytes);

@@ -465,7 +465,7 @@ struct Q4StreamLaunch {
     int tile_mode;          // 1: CTA b owns row pair-tiles [b*nrp/grid, (b+1)*nrp/grid) and its warps split them
     int nrp;                // row pair-tiles
     int depth;              // ring stages per warp
-    uint2* partials;        // [CTAs][2][32 lanes][4] (value, epoch) pairs
+    uint2* partials;        // [CTAs][2][32 lanes][4] (value, tag) pairs
     int* status;            // set non-zero when a bounded wait ran out
     // row-parallel mode (xworld > 0): finished tiles are not written to Y but pushed, as (value, 1) pairs,
     // into slot [xrank] of every rank's exchange buffer; then every rank adds the xworld slots of its own
@@ -475,8 +475,6 @@ struct Q4StreamLaunch {
     uint2* xpeer[8];        // rank r's exchange buffer (this rank's own for r == xrank), already offset to this launch's half
     int64_t xslot;          // uint2 per slot (>= M * N)
     uint32_t xlimit;        // polls of one element before giving up
-    int dbg;
-    unsigned long long* trace;   // debug: [gridDim.x][8] timestamps of warp 0, or null
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -692,13 +690,6 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
     const int M = p.M, ncols = 2 * M, nblk = p.nchunks * 2, D = p.depth;
     if (lane < 2) wrp[warp][lane] = -1;
     if (tid < 2) zero_pg[tid] = make_uint4(0, 0, 0, 0);
-#define Q4S_TRACE(slot)                                                                         \
-    if (p.trace && tid == 0) {                                                                  \
-        unsigned long long t_;                                                                  \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
-        p.trace[(size_t)blockIdx.x * 8 + (slot)] = t_;                                          \
-    }
-    Q4S_TRACE(0)
     unsigned char* ring = smem_raw + (size_t)warp * D * STAGE_BYTES;
     uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)Q4S_WARPS * D * STAGE_BYTES);
     float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nblk * ncols * 64);
@@ -739,14 +730,12 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         }
     }
 
-    Q4S_TRACE(1)
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    Q4S_TRACE(2)
 
     // ---- stage all of x as normalised hi/lo fp16 B fragments (same scheme as q4_linear_kernel)
     const int pk4 = p.nchunks * 16;                       // float4 per activation row, padding included
-    const int total4 = (p.dbg & 1) ? 0 : M * pk4;
+    const int total4 = M * pk4;
     float4 xv[NX > 0 ? NX : 1];
     uint32_t mx = 0;
     if (NX > 0) {
@@ -810,7 +799,6 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         }
     }
     __syncthreads();
-    Q4S_TRACE(3)
 
     // ---- stream this warp's run
     const float fA = (SUBN ? 16777216.f : 1.f) * inv_sc;     // 2^24: undo the subnormal weight encoding
@@ -859,37 +847,32 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             break;
         }
         const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)s * STAGE_BYTES);
-        if (!(p.dbg & 2)) {
 #pragma unroll
-            for (int q = 0; q < G; ++q) {
-                const uint4* un = st + q * Q4_UNIT_U4;
-                const uint4 w0 = un[lane], w1 = un[32 + lane], sv = un[64 + g];
-                const uint4 bf[2] = {xsp[0], xsp[1]};
-                const float4 cf[2] = {csp[0], csp[1]};
-                xsp += xstep;
-                csp += cstep;
-                const uint32_t wt[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
-                const uint32_t sw[2][2] = {{sv.x, sv.y}, {sv.z, sv.w}};
+        for (int q = 0; q < G; ++q) {
+            const uint4* un = st + q * Q4_UNIT_U4;
+            const uint4 w0 = un[lane], w1 = un[32 + lane], sv = un[64 + g];
+            const uint4 bf[2] = {xsp[0], xsp[1]};
+            const float4 cf[2] = {csp[0], csp[1]};
+            xsp += xstep;
+            csp += cstep;
+            const uint32_t wt[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
+            const uint32_t sw[2][2] = {{sv.x, sv.y}, {sv.z, sv.w}};
 #pragma unroll
-                for (int tile = 0; tile < 2; ++tile) {
-                    const float2 sA = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][0]));
-                    const float2 sB = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][1]));
+            for (int tile = 0; tile < 2; ++tile) {
+                const float2 sA = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][0]));
+                const float2 sB = __half22float2(*reinterpret_cast<const __half2*>(&sw[tile][1]));
 #pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        uint32_t a0[4], a1[4];
-                        q4_unpack<SUBN>(wt[tile][2 * b], a0);
-                        q4_unpack<SUBN>(wt[tile][2 * b + 1], a1);
-                        float d[4];
-                        mma16816(d, a0, bf[b].x, bf[b].y, cf[b].x, cf[b].y, cf[b].z, cf[b].w);
-                        mma16816(d, a1, bf[b].z, bf[b].w, d[0], d[1], d[2], d[3]);
-                        acc[tile][0] = fmaf(b ? sA.y : sA.x, d[0] + d[1], acc[tile][0]);
-                        acc[tile][1] = fmaf(b ? sB.y : sB.x, d[2] + d[3], acc[tile][1]);
-                    }
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t a0[4], a1[4];
+                    q4_unpack<SUBN>(wt[tile][2 * b], a0);
+                    q4_unpack<SUBN>(wt[tile][2 * b + 1], a1);
+                    float d[4];
+                    mma16816(d, a0, bf[b].x, bf[b].y, cf[b].x, cf[b].y, cf[b].z, cf[b].w);
+                    mma16816(d, a1, bf[b].z, bf[b].w, d[0], d[1], d[2], d[3]);
+                    acc[tile][0] = fmaf(b ? sA.y : sA.x, d[0] + d[1], acc[tile][0]);
+                    acc[tile][1] = fmaf(b ? sB.y : sB.x, d[2] + d[3], acc[tile][1]);
                 }
             }
-        } else {
-            xsp += G * xstep;
-            csp += G * cstep;
         }
         ++cg;
         __syncwarp();
@@ -900,7 +883,7 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             ++issued;
         }
         if (cg == gpr) {                                   // row pair-tile finished
-            if (!(p.dbg & 4)) flush(rp);
+            flush(rp);
             acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
             cg = 0;
             ++rp;
@@ -909,10 +892,8 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         }
         if (++s == D) { s = 0; parity ^= 1u; }
     }
-    Q4S_TRACE(4)
-    if (cg != 0 && !timed_out && !(p.dbg & 4)) flush(rp);  // the run ended inside a row pair-tile
+    if (cg != 0 && !timed_out) flush(rp);  // the run ended inside a row pair-tile
     __syncthreads();
-    Q4S_TRACE(5)
 
     // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
     // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
@@ -939,7 +920,6 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             q4s_cross_cta(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
         }
     }
-    Q4S_TRACE(6)
 
     // ---- row-parallel: add the ranks' partial outputs.  The tagged pairs need no flag and no grid
     // barrier: an element is ready when all xworld copies of it carry the tag.
