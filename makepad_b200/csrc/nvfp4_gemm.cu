@@ -124,20 +124,24 @@ __global__ void nvfp4_sf_tile_kernel(const uint8_t* __restrict__ sf, int64_t row
 
 static inline int ksteps_padded(int64_t K) { return (int)(((K + 63) / 64 + 3) / 4 * 4); }
 
-static cudaError_t sf_tile_launch(const uint8_t* sf, int64_t rows, int64_t K, int tile_rows, uint8_t* dst, cudaStream_t s)
+// tile_multiple: the number of tiles is rounded up to a multiple of it (2 for the activations: a CTA pair always
+// loads two 128-row slabs); the extra tiles are zero
+static cudaError_t sf_tile_launch(const uint8_t* sf, int64_t rows, int64_t K, int tile_rows, uint8_t* dst, cudaStream_t s, int tile_multiple = 1)
 {
     int atoms = (tile_rows + 127) / 128;
     int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+    tiles = (tiles + tile_multiple - 1) / tile_multiple * tile_multiple;
     int kp = ksteps_padded(K);
     int64_t total = tiles * kp * atoms * 128;
     nvfp4_sf_tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sf, rows, K, tile_rows, atoms, kp, total, dst);
     return cudaGetLastError();
 }
 
-static size_t sf_tiled_bytes(int64_t rows, int64_t K, int tile_rows)
+static size_t sf_tiled_bytes(int64_t rows, int64_t K, int tile_rows, int tile_multiple = 1)
 {
     int atoms = (tile_rows + 127) / 128;
     int64_t tiles = (rows + tile_rows - 1) / tile_rows;
+    tiles = (tiles + tile_multiple - 1) / tile_multiple * tile_multiple;
     return (size_t)tiles * ksteps_padded(K) * atoms * 512;
 }
 
@@ -243,6 +247,34 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+// registers -> this warp's 32 TMEM lanes: thread l writes lane l, register j goes to column +j
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                   "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// bounded spin on a phase parity without suspending the thread: for the hand-offs whose latency is on the critical path
+__device__ __forceinline__ bool bar_spin(uint32_t bar, uint32_t parity, uint32_t limit)
+{
+    for (uint32_t n = 0; n < limit; ++n) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 
 // K-major operand tile, SWIZZLE_128B: rows are 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
@@ -273,6 +305,7 @@ struct GemmParams {
     int m_tiles, n_tiles, k_blocks, ksteps_pad;
     float scale;             // tsA * tsB
     int* status;
+    int sfa_direct;          // 1: the activations' scale factors are read from their canonical [M][K/16] array (K % 256 == 0)
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -405,6 +438,266 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
+// the default kernel: scale factors written to TMEM by tcgen05.st, one accumulator
+// ---------------------------------------------------------------------------
+// Measured on B200: the tensor pipe takes what one thread issues strictly in order and queues almost nothing,
+// so every tcgen05.cp of scale factors (about 47 cycles, twelve per K block) and every cycle the issuing
+// thread spends between two MMAs is a bubble next to 4 x 112 cycles of math.  Here the MMA thread issues
+// nothing but MMAs and one commit per K block:
+//   * four WRITER warps move the scale factors shared memory -> registers -> TMEM (tcgen05.st, each warp its own
+//     lane quarter; every quarter holds the same copy, lane l column c = rows l + 32 c, as tcgen05.cp.32x128b.warpx4
+//     would have left it).  One TMEM buffer of 48 columns per pipeline stage: a stage's "full" barrier can only
+//     complete after the MMAs of its previous use have been committed, so the buffer is free whenever its stage is.
+//   * the MMA thread waits for the NEXT K block's barriers while the third MMA of the current one is running.
+//   * the 64 columns left beside two accumulators cannot hold four buffers, so there is ONE accumulator of
+//     224 columns; eight epilogue warps pull it into registers (112 columns per thread) and release it before
+//     they convert and store, which costs a few hundred cycles per tile instead of a second accumulator.
+constexpr int V2_THREADS = 448;               // TMA, MMA, 8 epilogue, 4 writer warps
+constexpr int V2_SF_COL = BN;                 // 224 .. 415: STAGES buffers of 48 columns
+constexpr int V2_SF_COLS = 48;                // [SFB: 4 K steps x 8 | SFA: 4 K steps x 4]
+constexpr int V2_EPI_COLS = BN / 2;           // columns per epilogue warp
+static_assert(V2_SF_COL + STAGES * V2_SF_COLS <= TMEM_COLS, "scale-factor buffers must fit beside the accumulator");
+static_assert(V2_EPI_COLS == 112, "the epilogue loads 3 x 32 + 16 columns");
+
+// One K block's scale factors of this thread's TMEM lane: r[0..31] = B's (K step ks, columns 8 ks .. 8 ks + 7: rows
+// lane + 32 c of the 224-row tile), r[32..47] = A's (columns 4 ks + c: rows lane + 32 c).  src points at the stage's
+// scale area + 16 * lane.  A's scales are either tiled like B's (512-byte atoms per K step) or, read directly from
+// the canonical array by TMA, 128 rows of 16 bytes: row r's four K steps are the four words at 16 r.
+__device__ __forceinline__ void load_sf_registers(const unsigned char* src, bool sfa_direct, uint32_t (&r)[48])
+{
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint4 b0 = *reinterpret_cast<const uint4*>(src + SFA_BYTES + ks * 1024);
+        const uint4 b1 = *reinterpret_cast<const uint4*>(src + SFA_BYTES + ks * 1024 + 512);
+        r[8 * ks + 0] = b0.x; r[8 * ks + 1] = b0.y; r[8 * ks + 2] = b0.z; r[8 * ks + 3] = b0.w;
+        r[8 * ks + 4] = b1.x; r[8 * ks + 5] = b1.y; r[8 * ks + 6] = b1.z; r[8 * ks + 7] = b1.w;
+    }
+    if (sfa_direct) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src + c * 512);     // row lane + 32 c
+            r[32 + c] = a.x; r[36 + c] = a.y; r[40 + c] = a.z; r[44 + c] = a.w;
+        }
+    } else {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint4 a = *reinterpret_cast<const uint4*>(src + ks * 512);
+            r[32 + 4 * ks + 0] = a.x; r[32 + 4 * ks + 1] = a.y; r[32 + 4 * ks + 2] = a.z; r[32 + 4 * ks + 3] = a.w;
+        }
+    }
+}
+
+#ifdef MPQ_FP4_PROF
+__device__ long long g_prof[1024][8];
+#endif
+__global__ void __launch_bounds__(V2_THREADS, 1)
+nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_sfa, const GemmParams p)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile int s_abort;
+    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bars = smem0 + STAGES * STAGE_BYTES;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES, bar_sf_ready = bars + 16 * STAGES,
+                   bar_acc_full = bars + 24 * STAGES, bar_acc_empty = bars + 24 * STAGES + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            bar_init(bar_full + 8 * s, 1);
+            bar_init(bar_empty + 8 * s, 5);        // the MMAs' commit + the four writer warps
+            bar_init(bar_sf_ready + 8 * s, 4);
+        }
+        bar_init(bar_acc_full, 1);
+        bar_init(bar_acc_empty, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x) {
+                const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+                const uint8_t* sfa_t = p.sfa + (size_t)mt * p.ksteps_pad * 512;
+                const uint8_t* sfb_t = p.sfb + (size_t)nt * p.ksteps_pad * 1024;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!bar_wait(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 3); s_abort = 1; break; }
+                    const uint32_t st = smem0 + stage * STAGE_BYTES, full = bar_full + 8 * stage;
+                    bar_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(st, &map_a, kb * (BK / 2), mt * BM, full);
+                    tma_load_2d(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN, full);
+                    if (p.sfa_direct) tma_load_2d(st + A_BYTES + B_BYTES, &map_sfa, kb * 16, mt * BM, full);   // [128 rows][16 scales]
+                    else bulk_load(st + A_BYTES + B_BYTES, sfa_t + (size_t)kb * SFA_BYTES, SFA_BYTES, full);
+                    bulk_load(st + A_BYTES + B_BYTES + SFA_BYTES, sfb_t + (size_t)kb * SFB_BYTES, SFB_BYTES, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            const int my_tiles = blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+            const long long total_kb = (long long)my_tiles * p.k_blocks;
+            long long done_kb = 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool seen = false;                         // the barriers of (stage, phase) have already been observed
+            bool ok = true;
+#ifdef MPQ_FP4_PROF
+            long long pw_acc = 0, pw_first = 0, pw_next = 0, pt0 = clock64(), pc;
+            unsigned long long g0, g1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
+#define P0 pc = clock64();
+#define P1(v) v += clock64() - pc;
+#else
+#define P0
+#define P1(v)
+#endif
+            for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
+                // the accumulator is free once the eight epilogue warps hold the previous tile in registers
+                P0
+                if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 4); s_abort = 1; break; }
+                P1(pw_acc)
+                tc_fence_after();
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!seen) {
+                        P0
+                        ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT) && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
+                        if (!ok) { atomicExch(p.status, 5); s_abort = 1; break; }
+                        tc_fence_after();
+                        P1(pw_first)
+                    }
+                    seen = false;
+                    const uint32_t st = smem0 + stage * STAGE_BYTES;
+                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
+                    const uint32_t sfb_t = tmem + V2_SF_COL + stage * V2_SF_COLS, sfa_t = sfb_t + 32;
+#pragma unroll
+                    for (int ks = 0; ks < 3; ++ks)         // +32 bytes along K inside the swizzle atom = +2 in the address field
+                        tc_mma_nvf4(tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, sfa_t + ks * 4, sfb_t + ks * 8, (kb | ks) ? 1u : 0u);
+                    // while those run: is the next K block (of this tile or the next one) ready?
+                    ++done_kb;
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == STAGES) { nstage = 0; nphase ^= 1u; }
+                    if (done_kb < total_kb) {
+                        P0
+                        ok = bar_spin(bar_sf_ready + 8 * nstage, nphase, SPIN_LIMIT) && bar_spin(bar_full + 8 * nstage, nphase, SPIN_LIMIT);
+                        if (!ok) { atomicExch(p.status, 5); s_abort = 1; break; }
+                        tc_fence_after();
+                        seen = true;
+                        P1(pw_next)
+                    }
+                    tc_mma_nvf4(tmem, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
+                    tc_commit(bar_empty + 8 * stage);      // the stage and its scale-factor buffer are free when these MMAs are done
+                    stage = nstage;
+                    phase = nphase;
+                }
+                if (!ok) break;
+                tc_commit(bar_acc_full);                   // accumulator complete
+            }
+#ifdef MPQ_FP4_PROF
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+            g_prof[blockIdx.x][0] = pw_acc; g_prof[blockIdx.x][1] = pw_first; g_prof[blockIdx.x][2] = pw_next;
+            g_prof[blockIdx.x][3] = clock64() - pt0; g_prof[blockIdx.x][4] = (long long)(g1 - g0);
+#endif
+        }
+    } else if (warp >= 10) {
+        // ---------------- scale-factor writers: warps 10..13, TMEM lane quarter = warp % 4 ----------------
+        const uint32_t lanes = (uint32_t)((warp & 3) * 32) << 16;
+        const unsigned char* sf_smem = smem_dyn + (smem0 - s2u(smem_dyn)) + A_BYTES + B_BYTES + lane * 16;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool live = true;
+#ifdef MPQ_FP4_PROF
+        long long ww = 0, wt0 = clock64(), pc;
+#endif
+        for (int tile = blockIdx.x; tile < total_tiles && live && !s_abort; tile += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                P0
+                if (!bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 8); s_abort = 1; } live = false; break; }
+                P1(ww)
+                const unsigned char* src = sf_smem + stage * STAGE_BYTES;
+                uint32_t r[48];
+                load_sf_registers(src, p.sfa_direct != 0, r);
+                // full[stage] can only have completed after the MMAs of the stage's previous use were committed:
+                // nobody reads this stage's TMEM buffer any more
+                tc_fence_after();
+                const uint32_t dst = tmem + lanes + V2_SF_COL + stage * V2_SF_COLS;
+                tc_st16(dst, r);
+                tc_st16(dst + 16, r + 16);
+                tc_st16(dst + 32, r + 32);
+                tc_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    bar_arrive(bar_sf_ready + 8 * stage);
+                    bar_arrive(bar_empty + 8 * stage);         // this warp no longer needs the stage's shared memory
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+#ifdef MPQ_FP4_PROF
+        if (warp == 10 && lane == 0) { g_prof[blockIdx.x][5] = ww; g_prof[blockIdx.x][6] = clock64() - wt0; }
+#endif
+    } else {
+        // ---------------- epilogue: warps 2..9; TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----------------
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x, ++local) {
+            const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
+            if (!bar_spin(bar_acc_full, (uint32_t)local & 1u, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 6); s_abort = 1; } break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + half * V2_EPI_COLS;
+            uint32_t r[V2_EPI_COLS];
+            tc_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tc_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tc_ld32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(&r[64]));
+            tc_ld16(taddr + 96, &r[96]);
+            tc_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar_acc_empty);          // the next tile's MMAs may overwrite the accumulator
+            const int row = mt * BM + quarter * 32 + lane;
+            if (row < p.M) {
+                const int col0 = nt * BN + half * V2_EPI_COLS;
+                __nv_bfloat16* crow = p.C + (size_t)row * p.N + col0;
+#pragma unroll
+                for (int v = 0; v < V2_EPI_COLS / 8; ++v) {
+                    uint4 o;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
+                    o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                    o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                    if (col0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + 8 * v) = o;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // the CTA-pair kernel: 256 x 224 tiles, tcgen05 cta_group::2
 // ---------------------------------------------------------------------------
 // Two CTAs of a cluster share one MMA: the leader (even rank) issues
@@ -434,6 +727,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
 __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// no memory ordering of its own: for hand-offs whose data went through tcgen05 fences (tensor memory), not shared memory
+__device__ __forceinline__ void bar_arrive_cluster_relaxed(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void bar_arrive_cluster(uint32_t cluster_addr)
 {
@@ -472,6 +770,7 @@ struct PairParams {
     int m_pairs, n_tiles, k_blocks, ksteps_pad;   // m_pairs = ceil(M / 256)
     float scale;
     int* status;
+    int sfa_direct;          // 1: the activations' scale factors are read from their canonical [M][K/16] array (K % 256 == 0)
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
@@ -609,6 +908,243 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 }
 
 // ---------------------------------------------------------------------------
+// CTA pairs with tcgen05.st scale factors: the default kernel where clusters of two can be scheduled
+// ---------------------------------------------------------------------------
+// nvfp4_gemm_kernel_v2's structure (writer warps, one accumulator drained into registers, look-ahead waits) on
+// 256 x 224 tiles of a CTA pair: each CTA loads its 128 rows of A and HALF of the B tile, which cuts the
+// L2 -> shared-memory traffic per flop by a third -- with the scale copies out of the way that traffic is what
+// bounds the single-CTA kernel.  A and B tiles are TMA loads with .cta_group::2 counted on the LEADER's full
+// barrier; the scale-factor slabs are plain bulk copies counted on each CTA's OWN barrier, which is what its
+// writer warps wait for; the writers of both CTAs then arrive on the leader's sf_ready barrier.  One TMEM
+// scale-factor buffer per pipeline stage: a CTA refills a stage only after the leader's commit for the stage's
+// previous use has reached it, so the buffer is free whenever its scale factors arrive.
+constexpr int Q_STAGES = 6;
+constexpr int Q_STAGE_BYTES = A_BYTES + P_BH_BYTES + SFA_BYTES + SFB_BYTES;     // 36864
+constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
+static_assert(V2_SF_COL + Q_STAGES * V2_SF_COLS <= TMEM_COLS, "scale-factor buffers must fit beside the accumulator");
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(V2_THREADS, 1)
+nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_sfa, const PairParams p, const uint8_t* __restrict__ sfa,
+                          const uint8_t* __restrict__ sfb)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ volatile int s_abort;
+    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bars = smem0 + Q_STAGES * Q_STAGE_BYTES;
+    // full: A and B of both CTAs (leader's is used); sf_full: this CTA's scale slabs; empty: commit + 4 local writers;
+    // sf_ready: 8 writer warps of the pair (leader's is used)
+    const uint32_t bar_full = bars, bar_sf_full = bars + 8 * Q_STAGES, bar_empty = bars + 16 * Q_STAGES,
+                   bar_sf_ready = bars + 24 * Q_STAGES, bar_acc_full = bars + 32 * Q_STAGES, bar_acc_empty = bars + 32 * Q_STAGES + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                 // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int total_tiles = p.m_pairs * p.n_tiles;
+    constexpr uint32_t AB_BYTES = A_BYTES + P_BH_BYTES, SF_BYTES = SFA_BYTES + SFB_BYTES;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < Q_STAGES; ++s) {
+            bar_init(bar_full + 8 * s, 1);
+            bar_init(bar_sf_full + 8 * s, 1);
+            bar_init(bar_empty + 8 * s, 5);
+            bar_init(bar_sf_ready + 8 * s, 8);
+        }
+        bar_init(bar_acc_full, 1);
+        bar_init(bar_acc_empty, 16);                         // 8 epilogue warps of each CTA
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // both CTAs' barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+
+    if (warp == 0) {
+        // ---------------- producer (both CTAs; the leader arms the shared full barrier) ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs) {
+                const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
+                const int mt128 = 2 * mp + (int)rank;
+                const uint8_t* sfa_t = sfa + (size_t)mt128 * p.ksteps_pad * 512;
+                const uint8_t* sfb_t = sfb + (size_t)nt * p.ksteps_pad * 1024;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+#ifdef MPQ_FP4_PROF
+                    long long pc = clock64();
+#endif
+                    if (!bar_spin(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 13); s_abort = 1; break; }
+#ifdef MPQ_FP4_PROF
+                    g_prof[blockIdx.x][7] += clock64() - pc;
+#endif
+                    const uint32_t st = smem0 + stage * Q_STAGE_BYTES, full = bar_full + 8 * stage, sf_full = bar_sf_full + 8 * stage;
+                    bar_expect_tx(sf_full, SF_BYTES);
+                    if (p.sfa_direct) tma_load_2d(st + AB_BYTES, &map_sfa, kb * 16, mt128 * BM, sf_full);      // [128 rows][16 scales]
+                    else bulk_load(st + AB_BYTES, sfa_t + (size_t)kb * SFA_BYTES, SFA_BYTES, sf_full);
+                    bulk_load(st + AB_BYTES + SFA_BYTES, sfb_t + (size_t)kb * SFB_BYTES, SFB_BYTES, sf_full);
+                    if (rank == 0) bar_expect_tx(full, 2 * AB_BYTES);
+                    tma_load_2d_pair(st, &map_a, kb * (BK / 2), mt128 * BM, full);
+                    tma_load_2d_pair(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN + (int)rank * (BN / 2), full);
+                    if (++stage == Q_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the leader only ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const int my_tiles = pair < total_tiles ? (total_tiles - 1 - pair) / npairs + 1 : 0;
+            const long long total_kb = (long long)my_tiles * p.k_blocks;
+            long long done_kb = 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool seen = false, ok = true;
+#ifdef MPQ_FP4_PROF
+            long long pw_acc = 0, pw_first = 0, pw_next = 0, pw_sf = 0, pt0 = clock64(), pc;
+            unsigned long long g0, g1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
+#endif
+            for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
+                P0
+                if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 14); s_abort = 1; break; }
+                P1(pw_acc)
+                tc_fence_after();
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!seen) {
+                        P0
+                        ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT) && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
+                        P1(pw_first)
+                        if (!ok) { atomicExch(p.status, 15); s_abort = 1; break; }
+                        tc_fence_after();
+                    }
+                    seen = false;
+                    const uint32_t st = smem0 + stage * Q_STAGE_BYTES;
+                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
+                    const uint32_t sfb_c = tmem + V2_SF_COL + stage * V2_SF_COLS, sfa_c = sfb_c + 32;
+#pragma unroll
+                    for (int ks = 0; ks < 3; ++ks)
+                        tc_mma_nvf4_pair(tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, sfa_c + ks * 4, sfb_c + ks * 8, (kb | ks) ? 1u : 0u);
+                    ++done_kb;
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == Q_STAGES) { nstage = 0; nphase ^= 1u; }
+                    if (done_kb < total_kb) {                 // while those run: is the next K block ready?
+                        P0
+                        ok = bar_spin(bar_sf_ready + 8 * nstage, nphase, SPIN_LIMIT);
+                        P1(pw_sf)
+                        P0
+                        ok = ok && bar_spin(bar_full + 8 * nstage, nphase, SPIN_LIMIT);
+                        P1(pw_next)
+                        if (!ok) { atomicExch(p.status, 15); s_abort = 1; break; }
+                        tc_fence_after();
+                        seen = true;
+                    }
+                    tc_mma_nvf4_pair(tmem, adesc + 6, bdesc + 6, idesc, sfa_c + 12, sfb_c + 24, 1u);
+                    tc_commit_pair(bar_empty + 8 * stage);       // both CTAs may refill the stage and its scale-factor buffer
+                    stage = nstage;
+                    phase = nphase;
+                }
+                if (!ok) break;
+                tc_commit_pair(bar_acc_full);                    // both CTAs' epilogues may read
+            }
+#ifdef MPQ_FP4_PROF
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+            g_prof[blockIdx.x][0] = pw_acc; g_prof[blockIdx.x][1] = pw_first; g_prof[blockIdx.x][2] = pw_next;
+            g_prof[blockIdx.x][3] = clock64() - pt0; g_prof[blockIdx.x][4] = (long long)(g1 - g0); g_prof[blockIdx.x][5] = pw_sf;
+#endif
+        }
+    } else if (warp >= 10) {
+        // ---------------- scale-factor writers: warps 10..13 of each CTA, TMEM lane quarter = warp % 4 ----------------
+        const uint32_t lanes = (uint32_t)((warp & 3) * 32) << 16;
+        const unsigned char* sf_smem = smem_dyn + (smem0 - s2u(smem_dyn)) + AB_BYTES + lane * 16;
+        const uint32_t leader_sf_ready = map_to_cta(bar_sf_ready, 0);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool live = true;
+        for (int tile = pair; tile < total_tiles && live && !s_abort; tile += npairs) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+#ifdef MPQ_FP4_PROF
+                long long pc = clock64();
+#endif
+                if (!bar_spin(bar_sf_full + 8 * stage, phase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 18); s_abort = 1; } live = false; break; }
+#ifdef MPQ_FP4_PROF
+                if (warp == 10 && lane == 0) g_prof[blockIdx.x][6] += clock64() - pc;
+#endif
+                const unsigned char* src = sf_smem + stage * Q_STAGE_BYTES;
+                uint32_t r[48];
+                load_sf_registers(src, p.sfa_direct != 0, r);
+                tc_fence_after();
+                const uint32_t dst = tmem + lanes + V2_SF_COL + stage * V2_SF_COLS;
+                tc_st16(dst, r);
+                tc_st16(dst + 16, r + 16);
+                tc_st16(dst + 32, r + 32);
+                tc_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) bar_arrive(bar_sf_ready + 8 * stage);
+                    else bar_arrive_cluster_relaxed(leader_sf_ready + 8 * stage);
+                    bar_arrive(bar_empty + 8 * stage);
+                }
+                if (++stage == Q_STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------- epilogue: warps 2..9 of each CTA, its own 128 rows ----------------
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
+        int local = 0;
+        for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs, ++local) {
+            const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
+            if (!bar_spin(bar_acc_full, (uint32_t)local & 1u, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 16); s_abort = 1; } break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + half * V2_EPI_COLS;
+            uint32_t r[V2_EPI_COLS];
+            tc_ld32(taddr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+            tc_ld32(taddr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+            tc_ld32(taddr + 64, *reinterpret_cast<uint32_t(*)[32]>(&r[64]));
+            tc_ld16(taddr + 96, &r[96]);
+            tc_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {                                       // the leader's MMA thread waits for all sixteen warps
+                if (rank == 0) bar_arrive(bar_acc_empty);
+                else bar_arrive_cluster_relaxed(leader_acc_empty);
+            }
+            const int row = (2 * mp + (int)rank) * BM + quarter * 32 + lane;
+            if (row < p.M) {
+                const int col0 = nt * BN + half * V2_EPI_COLS;
+                __nv_bfloat16* crow = p.C + (size_t)row * p.N + col0;
+#pragma unroll
+                for (int v = 0; v < V2_EPI_COLS / 8; ++v) {
+                    uint4 o;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
+                    o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                    o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                    if (col0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + 8 * v) = o;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                      // the peer's shared memory and barriers stay valid until both are done
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -638,6 +1174,19 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K
     cuuint32_t estr[2] = {1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// canonical scale factors [rows][K/16] bytes; box = 128 rows x 16 bytes (one K block), no swizzle, zero fill
+static bool make_sf_direct_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)(K / 16), (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(K / 16)};
+    cuuint32_t box[2] = {16u, (cuuint32_t)BM};
+    cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // tiled scale factors as a 2-D array of 512-byte atoms: `atoms` rows of 128 uint32; box = box_rows atoms
@@ -675,12 +1224,33 @@ static int pair_clusters(int sm_count)
     return cached;
 }
 
+static int pair_v2_clusters(int sm_count)
+{
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    cached = 0;
+    if (cudaFuncSetAttribute(nvfp4_gemm_pair_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count & ~1));
+    cfg.blockDim = dim3(V2_THREADS);
+    cfg.dynamicSmemBytes = Q_SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, nvfp4_gemm_pair_kernel_v2, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    cached = n;
+    return cached;
+}
+
 int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_t* a_codes, const uint8_t* a_sf, float ta,
                           int64_t M, uint16_t* c, int sm_count, cudaStream_t s, int* launches, std::string& err)
 {
     *launches = 0;
     const int64_t N = w.N, K = w.K;
-    size_t need = sf_tiled_bytes(M, K, BM);
+    size_t need = sf_tiled_bytes(M, K, BM, 2);
     if (scratch.sfa_bytes < need) {
         cudaDeviceSynchronize();
         cudaFree(scratch.sfa_tiled);
@@ -695,20 +1265,49 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
         if (e == cudaSuccess) e = cudaMemset(scratch.status, 0, sizeof(int));
         if (e != cudaSuccess) { err = std::string("status allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     }
-    cudaError_t e = sf_tile_launch(a_sf, M, K, BM, scratch.sfa_tiled, s);
-    *launches += 1;
-    if (e != cudaSuccess) { err = std::string("scale-factor tiling failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    // Kernel choice (MPQ_FP4_KERNEL, for experiments and the parity tests): "pair" (default where clusters of two can be
+    // scheduled) and "single" write the scale factors with tcgen05.st; "pair_cp" and "single_cp" are the older kernels that
+    // copy them with tcgen05.cp from the MMA thread.
+    const char* env = getenv("MPQ_FP4_KERNEL");
+    const std::string kind = env ? env : "pair";
+    // The tcgen05.st kernels read the activations' scale factors straight from the canonical array when a K block's 16
+    // bytes per row can be a TMA box (row pitch K/16 a multiple of 16 bytes); otherwise they are re-tiled first.
+    const bool direct = (kind == "pair" || kind == "single") && K % 256 == 0 && (reinterpret_cast<uintptr_t>(a_sf) & 15u) == 0;
+    cudaError_t e = cudaSuccess;
+    if (!direct) {
+        e = sf_tile_launch(a_sf, M, K, BM, scratch.sfa_tiled, s, 2);
+        *launches += 1;
+        if (e != cudaSuccess) { err = std::string("scale-factor tiling failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    }
 
-    CUtensorMap map_a, map_b;
-    if (!make_map(&map_a, a_codes, M, K, BM) || !make_map(&map_b, w.codes, N, K, BN)) {
+    CUtensorMap map_a, map_b, map_sfa;
+    if (!make_map(&map_a, a_codes, M, K, BM) || !make_map(&map_b, w.codes, N, K, BN) ||
+        !(direct ? make_sf_direct_map(&map_sfa, a_sf, M, K) : make_map(&map_sfa, a_codes, M, K, BM))) {
         err = "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, K a multiple of 32)";
         return MPQ_ERR_CUDA;
     }
-    // The CTA-pair kernel (tcgen05 cta_group::2) is correct but measured slightly slower than the single-CTA
-    // kernel at the prefill shape (93 vs 87 us): both are bound by the serial scale-copy + MMA issue of one
-    // thread, not by operand traffic.  It is kept selectable (MPQ_FP4_PAIR=1) and covered by a parity test.
-    const char* env = getenv("MPQ_FP4_PAIR");
-    const int clusters = (env && env[0] == '1') ? pair_clusters(sm_count) : 0;
+    if (kind == "pair") {
+        const int nclusters = pair_v2_clusters(sm_count);
+        if (nclusters > 0) {
+            CUtensorMap map_bh;
+            if (!make_map(&map_bh, w.codes, N, K, BN / 2)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
+            PairParams pp;
+            pp.C = reinterpret_cast<__nv_bfloat16*>(c);
+            pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
+            pp.m_pairs = (int)((M + 2 * BM - 1) / (2 * BM)); pp.n_tiles = (int)((N + BN - 1) / BN);
+            pp.k_blocks = (int)((K + BK - 1) / BK); pp.ksteps_pad = ksteps_padded(K);
+            pp.scale = ta * w.tensor_scale;
+            pp.status = scratch.status;
+            pp.sfa_direct = direct ? 1 : 0;
+            int grid = 2 * std::min(nclusters, pp.m_pairs * pp.n_tiles);
+            nvfp4_gemm_pair_kernel_v2<<<grid, V2_THREADS, Q_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, pp, scratch.sfa_tiled, w.sf_tiled);
+            *launches += 1;
+            e = cudaGetLastError();
+            if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+            return MPQ_OK;
+        }
+    }
+    const int clusters = kind == "pair_cp" ? pair_clusters(sm_count) : 0;
     if (clusters > 0) {
         // CTA-pair kernel: B is loaded in halves of 112 rows, the scale-factor slabs through tensor maps too
         CUtensorMap map_bh, map_sfa, map_sfb;
@@ -740,14 +1339,17 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     p.k_blocks = (int)((K + BK - 1) / BK); p.ksteps_pad = ksteps_padded(K);
     p.scale = ta * w.tensor_scale;
     p.status = scratch.status;
+    p.sfa_direct = direct ? 1 : 0;
     static bool configured = false;
     if (!configured) {
         e = cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(nvfp4_gemm_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
         configured = true;
     }
     int grid = std::min(sm_count, p.m_tiles * p.n_tiles);
-    nvfp4_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+    if (kind == "single_cp") nvfp4_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);       // scale factors by tcgen05.cp, two accumulators
+    else nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, p);
     *launches += 1;
     e = cudaGetLastError();
     if (e != cudaSuccess) { err = std::string("nvfp4_gemm_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
