@@ -7,23 +7,22 @@
 // No reference source exists for this path (the makepad/makepad snapshot has no
 // quantised-linear code); the operator is specified by the task configuration.
 //
-// TILE.  One CTA per SM loops over 128 x 224 output tiles (14336 = 64 * 224; two
-// fp32 accumulators of 224 columns plus the scale factors fit the 512 TMEM
-// columns, so the epilogue of one tile overlaps the MMAs of the next).  K is
-// consumed in blocks of 256 elements = 128 bytes per row = one 128-byte-swizzle
-// atom = four tcgen05.mma (K = 64 each).
+// TILE.  Output tiles are 224 columns wide (14336 = 64 * 224); a CTA owns 128 rows of one (TMEM has 128 lanes).
+// K is consumed in blocks of 256 elements = 128 bytes per row = one 128-byte-swizzle atom = four tcgen05.mma
+// (K = 64 each).  Two kernels share that geometry: nvfp4_gemm_pair_kernel_v2 (default; a cluster of two CTAs on
+// 256 x 224 tiles with tcgen05 cta_group::2) and nvfp4_gemm_kernel_v2 (one CTA per tile, used where clusters of
+// two cannot be scheduled).
 //
-// ROLES.  warp 0: TMA producer (A tile, B tile, the two scale-factor slabs).
-//         warp 1: TMEM allocation, tcgen05.cp of the scale factors, MMA issue.
-//         warps 2..5: epilogue (tcgen05.ld -> scale -> bf16 -> global).
+// ROLES (both kernels).  warp 0: TMA producer.  warp 1: TMEM allocation, MMA issue.  warps 2..9: epilogue
+// (tcgen05.ld of the whole accumulator into registers, release, then scale -> bf16 -> global).  warps 10..13:
+// scale-factor writers (shared memory -> registers -> TMEM by tcgen05.st).
 //
-// CODES need no repack: canonical [rows][K/2] bytes are K-major, which is what
-// the MMA's shared-memory descriptor (K-major, SWIZZLE_128B) wants; TMA applies
-// the swizzle.  SCALE FACTORS are re-tiled so that the 512 bytes one
-// tcgen05.cp.32x128b.warpx4 moves are contiguous: for 128 rows and one K step
-// of 64 (four scales per row), byte (row%32)*16 + (row/32)*4 + j.  A's slabs are
-// per 128 rows; B's are per 224-row output tile (two such atoms, the second
-// three-quarters full).
+// CODES need no repack: canonical [rows][K/2] bytes are K-major, which is what the MMA's shared-memory descriptor
+// (K-major, SWIZZLE_128B) wants; TMA applies the swizzle.  SCALE FACTORS of the weights are re-tiled once into
+// 512-byte atoms, one per 128 rows and K step of 64: byte (row%32)*16 + (row/32)*4 + j (j = the step's four scales),
+// which is, per TMEM lane, the four columns the tensor core reads; B's slabs are per 224-row tile (two atoms, the
+// second three-quarters full).  The activations' scale factors are fetched from their canonical array by TMA
+// (16 bytes per row and K block) when K is a multiple of 256, else re-tiled per call like the weights'.
 //
 // No TMA load here uses cluster multicast.
 #include <cuda.h>
@@ -90,8 +89,6 @@ constexpr int SFB_BYTES = 4 * 2 * 512;                     // four K steps x two
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 51200
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int TMEM_COLS = 512;
-constexpr int ACC_COL0 = 0, ACC_COL1 = BN, SFA_COL = 2 * BN, SFB_COL = 2 * BN + 16;   // 448, 464..495
-constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;     // polls of one mbarrier before the kernel gives up and reports it
 
 // scale factors of `rows` rows, tiled for tiles of `tile_rows` rows (128 for A, 224 for B):
@@ -219,10 +216,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc)
-{
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
                                             uint32_t sfb, uint32_t accumulate)
 {
@@ -264,6 +257,13 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r)
                    "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // bounded spin on a phase parity without suspending the thread: for the hand-offs whose latency is on the critical path
 __device__ __forceinline__ bool bar_spin(uint32_t bar, uint32_t parity, uint32_t limit)
 {
@@ -287,15 +287,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
     return d;
 }
-// scale-factor atom: 32 rows of 16 bytes, no swizzle; 8-row core matrices 128 bytes apart
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr)
-{
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFF);
-    d |= (uint64_t)(128 >> 4) << 32;                // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;
-    return d;
-}
 
 struct GemmParams {
     const uint8_t* sfa;      // tiled
@@ -308,147 +299,19 @@ struct GemmParams {
     int sfa_direct;          // 1: the activations' scale factors are read from their canonical [M][K/16] array (K % 256 == 0)
 };
 
-__global__ void __launch_bounds__(THREADS, 1)
-nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p)
-{
-    extern __shared__ unsigned char smem_dyn[];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ volatile int s_abort;
-    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;          // SWIZZLE_128B tiles need 1024-byte alignment
-    const uint32_t bars = smem0 + STAGES * STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
-    const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES, bar_acc_full = bars + 16 * STAGES,
-                   bar_acc_empty = bars + 16 * STAGES + 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
-
-    if (threadIdx.x == 0) {
-        s_abort = 0;
-        for (int s = 0; s < STAGES; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { bar_init(bar_acc_full + 8 * b, 1); bar_init(bar_acc_empty + 8 * b, 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = s_tmem_base;
-
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x) {
-                const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-                const uint8_t* sfa_t = p.sfa + (size_t)mt * p.ksteps_pad * 512;
-                const uint8_t* sfb_t = p.sfb + (size_t)nt * p.ksteps_pad * 1024;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!bar_wait(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 3); s_abort = 1; break; }
-                    const uint32_t st = smem0 + stage * STAGE_BYTES, full = bar_full + 8 * stage;
-                    bar_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(st, &map_a, kb * (BK / 2), mt * BM, full);
-                    tma_load_2d(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN, full);
-                    bulk_load(st + A_BYTES + B_BYTES, sfa_t + (size_t)kb * SFA_BYTES, SFA_BYTES, full);
-                    bulk_load(st + A_BYTES + B_BYTES + SFA_BYTES, sfb_t + (size_t)kb * SFB_BYTES, SFB_BYTES, full);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            // instruction descriptor: A,B = e2m1 (1), K-major, N = BN, scale type ue4m3 (0), M = 128, K = 64 dense
-            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            int stage = 0, abuf = 0, local = 0;
-            uint32_t phase = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x, ++local) {
-                abuf = local & 1;
-                const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
-                if (!bar_wait(bar_acc_empty + 8 * abuf, aphase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 4); s_abort = 1; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem + (abuf ? ACC_COL1 : ACC_COL0);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!bar_wait(bar_full + 8 * stage, phase, SPIN_LIMIT)) { atomicExch(p.status, 5); s_abort = 1; break; }
-                    tc_fence_after();
-                    const uint32_t st = smem0 + stage * STAGE_BYTES;
-                    const uint32_t sfa_s = st + A_BYTES + B_BYTES, sfb_s = sfa_s + SFA_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        tc_cp_sf(tmem + SFA_COL + ks * 4, smem_desc_sf(sfa_s + ks * 512));
-                        tc_cp_sf(tmem + SFB_COL + ks * 8, smem_desc_sf(sfb_s + ks * 1024));
-                        tc_cp_sf(tmem + SFB_COL + ks * 8 + 4, smem_desc_sf(sfb_s + ks * 1024 + 512));
-                    }
-                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)        // +32 bytes along K inside the swizzle atom = +2 in the address field
-                        tc_mma_nvf4(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, tmem + SFA_COL + ks * 4, tmem + SFB_COL + ks * 8,
-                                    (kb | ks) ? 1u : 0u);
-                    tc_commit(bar_empty + 8 * stage);      // the stage may be refilled when these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                }
-                tc_commit(bar_acc_full + 8 * abuf);        // accumulator complete
-            }
-        }
-    } else {
-        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
-        const int quarter = warp & 3;
-        int local = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !s_abort; tile += gridDim.x, ++local) {
-            const int nt = tile / p.m_tiles, mt = tile - nt * p.m_tiles;
-            const int abuf = local & 1;
-            const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
-            if (!bar_wait(bar_acc_full + 8 * abuf, aphase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 6); s_abort = 1; } break; }
-            tc_fence_after();
-            const int row = mt * BM + quarter * 32 + lane;
-            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (abuf ? ACC_COL1 : ACC_COL0);
-            __nv_bfloat16* crow = p.C + (size_t)row * p.N + (size_t)nt * BN;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tc_ld32(taddr + c0, r);
-                tc_ld_wait();
-                if (row < p.M) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 o;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
-                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                        if (nt * BN + c0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = o;
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) bar_arrive(bar_acc_empty + 8 * abuf);
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-    }
-}
-
 // ---------------------------------------------------------------------------
-// the default kernel: scale factors written to TMEM by tcgen05.st, one accumulator
+// one CTA per tile: scale factors written to TMEM by tcgen05.st, one accumulator
 // ---------------------------------------------------------------------------
 // Measured on B200: the tensor pipe takes what one thread issues strictly in order and queues almost nothing,
-// so every tcgen05.cp of scale factors (about 47 cycles, twelve per K block) and every cycle the issuing
-// thread spends between two MMAs is a bubble next to 4 x 112 cycles of math.  Here the MMA thread issues
-// nothing but MMAs and one commit per K block:
+// so every tcgen05.cp of scale factors (about 47 cycles each, twelve per K block, when issued from the MMA thread)
+// and every cycle the issuing thread spends between two MMAs is a bubble next to 4 x 112 cycles of math.  Here the
+// MMA thread issues nothing but MMAs and one commit per K block:
 //   * four WRITER warps move the scale factors shared memory -> registers -> TMEM (tcgen05.st, each warp its own
 //     lane quarter; every quarter holds the same copy, lane l column c = rows l + 32 c, as tcgen05.cp.32x128b.warpx4
 //     would have left it).  One TMEM buffer of 48 columns per pipeline stage: a stage's "full" barrier can only
 //     complete after the MMAs of its previous use have been committed, so the buffer is free whenever its stage is.
-//   * the MMA thread waits for the NEXT K block's barriers while the third MMA of the current one is running.
+//   * the MMA thread looks at the NEXT K block's barriers while the third MMA of the current one is running (one
+//     non-blocking test: if they are not complete yet, the last MMA and the commit that frees the stage go first).
 //   * the 64 columns left beside two accumulators cannot hold four buffers, so there is ONE accumulator of
 //     224 columns; eight epilogue warps pull it into registers (112 columns per thread) and release it before
 //     they convert and store, which costs a few hundred cycles per tile instead of a second accumulator.
@@ -487,9 +350,6 @@ __device__ __forceinline__ void load_sf_registers(const unsigned char* src, bool
     }
 }
 
-#ifdef MPQ_FP4_PROF
-__device__ long long g_prof[1024][8];
-#endif
 __global__ void __launch_bounds__(V2_THREADS, 1)
 nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ CUtensorMap map_sfa, const GemmParams p)
@@ -557,29 +417,15 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
             uint32_t phase = 0;
             bool seen = false;                         // the barriers of (stage, phase) have already been observed
             bool ok = true;
-#ifdef MPQ_FP4_PROF
-            long long pw_acc = 0, pw_first = 0, pw_next = 0, pt0 = clock64(), pc;
-            unsigned long long g0, g1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
-#define P0 pc = clock64();
-#define P1(v) v += clock64() - pc;
-#else
-#define P0
-#define P1(v)
-#endif
             for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
                 // the accumulator is free once the eight epilogue warps hold the previous tile in registers
-                P0
                 if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 4); s_abort = 1; break; }
-                P1(pw_acc)
                 tc_fence_after();
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!seen) {
-                        P0
                         ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT) && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
                         if (!ok) { atomicExch(p.status, 5); s_abort = 1; break; }
                         tc_fence_after();
-                        P1(pw_first)
                     }
                     seen = false;
                     const uint32_t st = smem0 + stage * STAGE_BYTES;
@@ -593,13 +439,9 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
                     int nstage = stage + 1;
                     uint32_t nphase = phase;
                     if (nstage == STAGES) { nstage = 0; nphase ^= 1u; }
-                    if (done_kb < total_kb) {
-                        P0
-                        ok = bar_spin(bar_sf_ready + 8 * nstage, nphase, SPIN_LIMIT) && bar_spin(bar_full + 8 * nstage, nphase, SPIN_LIMIT);
-                        if (!ok) { atomicExch(p.status, 5); s_abort = 1; break; }
-                        tc_fence_after();
-                        seen = true;
-                        P1(pw_next)
+                    if (done_kb < total_kb && bar_test(bar_sf_ready + 8 * nstage, nphase) && bar_test(bar_full + 8 * nstage, nphase)) {
+                        tc_fence_after();                  // seen now, while MMAs are queued; if not ready, the last MMA and
+                        seen = true;                       // the commit that frees this stage must not wait for it
                     }
                     tc_mma_nvf4(tmem, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
                     tc_commit(bar_empty + 8 * stage);      // the stage and its scale-factor buffer are free when these MMAs are done
@@ -609,11 +451,6 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 if (!ok) break;
                 tc_commit(bar_acc_full);                   // accumulator complete
             }
-#ifdef MPQ_FP4_PROF
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
-            g_prof[blockIdx.x][0] = pw_acc; g_prof[blockIdx.x][1] = pw_first; g_prof[blockIdx.x][2] = pw_next;
-            g_prof[blockIdx.x][3] = clock64() - pt0; g_prof[blockIdx.x][4] = (long long)(g1 - g0);
-#endif
         }
     } else if (warp >= 10) {
         // ---------------- scale-factor writers: warps 10..13, TMEM lane quarter = warp % 4 ----------------
@@ -622,14 +459,9 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
         int stage = 0;
         uint32_t phase = 0;
         bool live = true;
-#ifdef MPQ_FP4_PROF
-        long long ww = 0, wt0 = clock64(), pc;
-#endif
         for (int tile = blockIdx.x; tile < total_tiles && live && !s_abort; tile += gridDim.x) {
             for (int kb = 0; kb < p.k_blocks; ++kb) {
-                P0
                 if (!bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 8); s_abort = 1; } live = false; break; }
-                P1(ww)
                 const unsigned char* src = sf_smem + stage * STAGE_BYTES;
                 uint32_t r[48];
                 load_sf_registers(src, p.sfa_direct != 0, r);
@@ -650,9 +482,6 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
         }
-#ifdef MPQ_FP4_PROF
-        if (warp == 10 && lane == 0) { g_prof[blockIdx.x][5] = ww; g_prof[blockIdx.x][6] = clock64() - wt0; }
-#endif
     } else {
         // ---------------- epilogue: warps 2..9; TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----------------
         const int quarter = warp & 3, half = (warp - 2) >> 2;
@@ -698,19 +527,12 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
 }
 
 // ---------------------------------------------------------------------------
-// the CTA-pair kernel: 256 x 224 tiles, tcgen05 cta_group::2
+// CTA pairs: 256 x 224 tiles, tcgen05 cta_group::2
 // ---------------------------------------------------------------------------
-// Two CTAs of a cluster share one MMA: the leader (even rank) issues
-// tcgen05.mma.cta_group::2 with M = 256; each CTA holds its own 128 rows of A, HALF of the B tile (112
-// rows) and its own accumulator, so a CTA loads 36 KB per K block instead of 51 KB and the tensor core
-// reads half as much B from its own shared memory.  Every load is a TMA tile load with .cta_group::2 (no
-// multicast) whose bytes are counted on the LEADER's full barrier; the leader's tcgen05.commit releases
-// the stage in both CTAs.  Scale factors: each CTA copies A's for its own rows and B's for all 224
-// columns into its own TMEM.
-constexpr int P_STAGES = 5;
+// Two CTAs of a cluster share one MMA: the leader (even rank) issues tcgen05.mma.cta_group::2 with M = 256; each CTA
+// holds its own 128 rows of A, HALF of the B tile (112 rows) and its own accumulator, so a CTA loads 36 KB per K block
+// instead of 51 KB.  The helpers below are the cluster-scope pieces.
 constexpr int P_BH_BYTES = (BN / 2) * BK / 2;                                    // 14336: half of the B tile
-constexpr int P_STAGE_BYTES = A_BYTES + P_BH_BYTES + SFA_BYTES + SFB_BYTES;     // 36864
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
@@ -748,10 +570,6 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
-__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc)
-{
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
                                                  uint32_t sfb, uint32_t accumulate)
 {
@@ -773,142 +591,8 @@ struct PairParams {
     int sfa_direct;          // 1: the activations' scale factors are read from their canonical [M][K/16] array (K % 256 == 0)
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb, const PairParams p)
-{
-    extern __shared__ unsigned char smem_dyn[];
-    __shared__ uint32_t s_tmem_base;
-    __shared__ volatile int s_abort;
-    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t bars = smem0 + P_STAGES * P_STAGE_BYTES;
-    const uint32_t bar_full = bars, bar_empty = bars + 8 * P_STAGES, bar_acc_full = bars + 16 * P_STAGES,
-                   bar_acc_empty = bars + 16 * P_STAGES + 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();                 // 0 = leader of the pair
-    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int total_tiles = p.m_pairs * p.n_tiles;
-
-    if (threadIdx.x == 0) {
-        s_abort = 0;
-        for (int s = 0; s < P_STAGES; ++s) { bar_init(bar_full + 8 * s, 1); bar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { bar_init(bar_acc_full + 8 * b, 1); bar_init(bar_acc_empty + 8 * b, 8); }   // 4 epilogue warps of each CTA
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();                                      // both CTAs' barriers exist before anyone signals them
-    tc_fence_after();
-    const uint32_t tmem = s_tmem_base;
-
-    if (warp == 0) {
-        // ---------------- TMA producer (both CTAs; the leader arms the shared full barrier) ----------------
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs) {
-                const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
-                const int mt128 = 2 * mp + (int)rank;
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!bar_wait(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 13); s_abort = 1; break; }
-                    const uint32_t st = smem0 + stage * P_STAGE_BYTES, full = bar_full + 8 * stage;
-                    if (rank == 0) bar_expect_tx(full, 2 * P_STAGE_BYTES);
-                    tma_load_2d_pair(st, &map_a, kb * (BK / 2), mt128 * BM, full);
-                    tma_load_2d_pair(st + A_BYTES, &map_b, kb * (BK / 2), nt * BN + (int)rank * (BN / 2), full);
-                    tma_load_2d_pair(st + A_BYTES + P_BH_BYTES, &map_sfa, 0, mt128 * p.ksteps_pad + kb * 4, full);
-                    tma_load_2d_pair(st + A_BYTES + P_BH_BYTES + SFA_BYTES, &map_sfb, 0, (nt * p.ksteps_pad + kb * 4) * 2, full);
-                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer: the leader only ----------------
-        if (lane == 0 && rank == 0) {
-            // A,B = e2m1, K-major, N = 224, scale type ue4m3, M = 256 across the pair, K = 64 dense
-            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-            int stage = 0, local = 0;
-            uint32_t phase = 0;
-            for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs, ++local) {
-                const int abuf = local & 1;
-                const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
-                if (!bar_wait(bar_acc_empty + 8 * abuf, aphase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 14); s_abort = 1; break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem + (abuf ? ACC_COL1 : ACC_COL0);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!bar_wait(bar_full + 8 * stage, phase, SPIN_LIMIT)) { atomicExch(p.status, 15); s_abort = 1; break; }
-                    tc_fence_after();
-                    const uint32_t st = smem0 + stage * P_STAGE_BYTES;
-                    const uint32_t sfa_s = st + A_BYTES + P_BH_BYTES, sfb_s = sfa_s + SFA_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        tc_cp_sf_pair(tmem + SFA_COL + ks * 4, smem_desc_sf(sfa_s + ks * 512));
-                        tc_cp_sf_pair(tmem + SFB_COL + ks * 8, smem_desc_sf(sfb_s + ks * 1024));
-                        tc_cp_sf_pair(tmem + SFB_COL + ks * 8 + 4, smem_desc_sf(sfb_s + ks * 1024 + 512));
-                    }
-                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        tc_mma_nvf4_pair(d_tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, tmem + SFA_COL + ks * 4, tmem + SFB_COL + ks * 8,
-                                         (kb | ks) ? 1u : 0u);
-                    tc_commit_pair(bar_empty + 8 * stage);       // both CTAs may refill the stage
-                    if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
-                }
-                tc_commit_pair(bar_acc_full + 8 * abuf);         // both CTAs' epilogues may read
-            }
-        }
-    } else {
-        // ---------------- epilogue: warps 2..5 of each CTA, its own 128 rows ----------------
-        const int quarter = warp & 3;
-        const uint32_t leader_acc_empty = map_to_cta(bar_acc_empty, 0);
-        int local = 0;
-        for (int tile = pair; tile < total_tiles && !s_abort; tile += npairs, ++local) {
-            const int nt = tile / p.m_pairs, mp = tile - nt * p.m_pairs;
-            const int abuf = local & 1;
-            const uint32_t aphase = (uint32_t)(local >> 1) & 1u;
-            if (!bar_wait(bar_acc_full + 8 * abuf, aphase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 16); s_abort = 1; } break; }
-            tc_fence_after();
-            const int row = (2 * mp + (int)rank) * BM + quarter * 32 + lane;
-            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (abuf ? ACC_COL1 : ACC_COL0);
-            __nv_bfloat16* crow = p.C + (size_t)row * p.N + (size_t)nt * BN;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tc_ld32(taddr + c0, r);
-                tc_ld_wait();
-                if (row < p.M) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 o;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
-                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                        if (nt * BN + c0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + c0 + 8 * v) = o;
-                    }
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) bar_arrive_cluster(leader_acc_empty + 8 * abuf);   // the leader's MMA warp waits for all eight warps
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync_all();                                      // the peer's shared memory and barriers stay valid until both are done
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-    }
-}
-
 // ---------------------------------------------------------------------------
-// CTA pairs with tcgen05.st scale factors: the default kernel where clusters of two can be scheduled
+// the default kernel where clusters of two can be scheduled
 // ---------------------------------------------------------------------------
 // nvfp4_gemm_kernel_v2's structure (writer warps, one accumulator drained into registers, look-ahead waits) on
 // 256 x 224 tiles of a CTA pair: each CTA loads its 128 rows of A and HALF of the B tile, which cuts the
@@ -976,13 +660,7 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                 const uint8_t* sfa_t = sfa + (size_t)mt128 * p.ksteps_pad * 512;
                 const uint8_t* sfb_t = sfb + (size_t)nt * p.ksteps_pad * 1024;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-#ifdef MPQ_FP4_PROF
-                    long long pc = clock64();
-#endif
                     if (!bar_spin(bar_empty + 8 * stage, phase ^ 1u, SPIN_LIMIT)) { atomicExch(p.status, 13); s_abort = 1; break; }
-#ifdef MPQ_FP4_PROF
-                    g_prof[blockIdx.x][7] += clock64() - pc;
-#endif
                     const uint32_t st = smem0 + stage * Q_STAGE_BYTES, full = bar_full + 8 * stage, sf_full = bar_sf_full + 8 * stage;
                     bar_expect_tx(sf_full, SF_BYTES);
                     if (p.sfa_direct) tma_load_2d(st + AB_BYTES, &map_sfa, kb * 16, mt128 * BM, sf_full);      // [128 rows][16 scales]
@@ -1005,21 +683,12 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
             int stage = 0;
             uint32_t phase = 0;
             bool seen = false, ok = true;
-#ifdef MPQ_FP4_PROF
-            long long pw_acc = 0, pw_first = 0, pw_next = 0, pw_sf = 0, pt0 = clock64(), pc;
-            unsigned long long g0, g1;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
-#endif
             for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
-                P0
                 if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 14); s_abort = 1; break; }
-                P1(pw_acc)
                 tc_fence_after();
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!seen) {
-                        P0
                         ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT) && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
-                        P1(pw_first)
                         if (!ok) { atomicExch(p.status, 15); s_abort = 1; break; }
                         tc_fence_after();
                     }
@@ -1034,16 +703,9 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                     int nstage = stage + 1;
                     uint32_t nphase = phase;
                     if (nstage == Q_STAGES) { nstage = 0; nphase ^= 1u; }
-                    if (done_kb < total_kb) {                 // while those run: is the next K block ready?
-                        P0
-                        ok = bar_spin(bar_sf_ready + 8 * nstage, nphase, SPIN_LIMIT);
-                        P1(pw_sf)
-                        P0
-                        ok = ok && bar_spin(bar_full + 8 * nstage, nphase, SPIN_LIMIT);
-                        P1(pw_next)
-                        if (!ok) { atomicExch(p.status, 15); s_abort = 1; break; }
-                        tc_fence_after();
-                        seen = true;
+                    if (done_kb < total_kb && bar_test(bar_sf_ready + 8 * nstage, nphase) && bar_test(bar_full + 8 * nstage, nphase)) {
+                        tc_fence_after();                  // seen now, while MMAs are queued; if not ready, the last MMA and
+                        seen = true;                       // the commit that frees this stage must not wait for it
                     }
                     tc_mma_nvf4_pair(tmem, adesc + 6, bdesc + 6, idesc, sfa_c + 12, sfb_c + 24, 1u);
                     tc_commit_pair(bar_empty + 8 * stage);       // both CTAs may refill the stage and its scale-factor buffer
@@ -1053,11 +715,6 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                 if (!ok) break;
                 tc_commit_pair(bar_acc_full);                    // both CTAs' epilogues may read
             }
-#ifdef MPQ_FP4_PROF
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
-            g_prof[blockIdx.x][0] = pw_acc; g_prof[blockIdx.x][1] = pw_first; g_prof[blockIdx.x][2] = pw_next;
-            g_prof[blockIdx.x][3] = clock64() - pt0; g_prof[blockIdx.x][4] = (long long)(g1 - g0); g_prof[blockIdx.x][5] = pw_sf;
-#endif
         }
     } else if (warp >= 10) {
         // ---------------- scale-factor writers: warps 10..13 of each CTA, TMEM lane quarter = warp % 4 ----------------
@@ -1069,13 +726,7 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
         bool live = true;
         for (int tile = pair; tile < total_tiles && live && !s_abort; tile += npairs) {
             for (int kb = 0; kb < p.k_blocks; ++kb) {
-#ifdef MPQ_FP4_PROF
-                long long pc = clock64();
-#endif
                 if (!bar_spin(bar_sf_full + 8 * stage, phase, SPIN_LIMIT)) { if (lane == 0) { atomicExch(p.status, 18); s_abort = 1; } live = false; break; }
-#ifdef MPQ_FP4_PROF
-                if (warp == 10 && lane == 0) g_prof[blockIdx.x][6] += clock64() - pc;
-#endif
                 const unsigned char* src = sf_smem + stage * Q_STAGE_BYTES;
                 uint32_t r[48];
                 load_sf_registers(src, p.sfa_direct != 0, r);
@@ -1189,40 +840,8 @@ static bool make_sf_direct_map(CUtensorMap* map, const void* base, int64_t rows,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// tiled scale factors as a 2-D array of 512-byte atoms: `atoms` rows of 128 uint32; box = box_rows atoms
-static bool make_sf_map(CUtensorMap* map, const void* base, int64_t atoms, int box_rows)
-{
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {128, (cuuint64_t)atoms};
-    cuuint64_t strides[1] = {512};
-    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1u, 1u};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 // CTA pairs the device can keep resident at once (0: the pair kernel cannot be used)
-static int pair_clusters(int sm_count)
-{
-    static int cached = -1;
-    if (cached >= 0) return cached;
-    cached = 0;
-    if (cudaFuncSetAttribute(nvfp4_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(sm_count & ~1));
-    cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = P_SMEM_BYTES;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, nvfp4_gemm_pair_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
-    cached = n;
-    return cached;
-}
 
 static int pair_v2_clusters(int sm_count)
 {
@@ -1250,88 +869,60 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
 {
     *launches = 0;
     const int64_t N = w.N, K = w.K;
-    size_t need = sf_tiled_bytes(M, K, BM, 2);
-    if (scratch.sfa_bytes < need) {
-        cudaDeviceSynchronize();
-        cudaFree(scratch.sfa_tiled);
-        scratch.sfa_tiled = nullptr;
-        scratch.sfa_bytes = 0;
-        cudaError_t e = cudaMalloc(&scratch.sfa_tiled, need);
-        if (e != cudaSuccess) { err = std::string("scratch allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
-        scratch.sfa_bytes = need;
-    }
     if (!scratch.status) {
         cudaError_t e = cudaMalloc(&scratch.status, sizeof(int));
         if (e == cudaSuccess) e = cudaMemset(scratch.status, 0, sizeof(int));
         if (e != cudaSuccess) { err = std::string("status allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     }
-    // Kernel choice (MPQ_FP4_KERNEL, for experiments and the parity tests): "pair" (default where clusters of two can be
-    // scheduled) and "single" write the scale factors with tcgen05.st; "pair_cp" and "single_cp" are the older kernels that
-    // copy them with tcgen05.cp from the MMA thread.
-    const char* env = getenv("MPQ_FP4_KERNEL");
-    const std::string kind = env ? env : "pair";
-    // The tcgen05.st kernels read the activations' scale factors straight from the canonical array when a K block's 16
-    // bytes per row can be a TMA box (row pitch K/16 a multiple of 16 bytes); otherwise they are re-tiled first.
-    const bool direct = (kind == "pair" || kind == "single") && K % 256 == 0 && (reinterpret_cast<uintptr_t>(a_sf) & 15u) == 0;
+    // The activations' scale factors are read straight from the canonical [M][K/16] array when a K block's 16 bytes per
+    // row can be a TMA box (row pitch a multiple of 16 bytes); otherwise they are re-tiled first, like the weights'.
+    const bool direct = K % 256 == 0 && (reinterpret_cast<uintptr_t>(a_sf) & 15u) == 0;
     cudaError_t e = cudaSuccess;
     if (!direct) {
+        size_t need = sf_tiled_bytes(M, K, BM, 2);
+        if (scratch.sfa_bytes < need) {
+            cudaDeviceSynchronize();
+            cudaFree(scratch.sfa_tiled);
+            scratch.sfa_tiled = nullptr;
+            scratch.sfa_bytes = 0;
+            e = cudaMalloc(&scratch.sfa_tiled, need);
+            if (e != cudaSuccess) { err = std::string("scratch allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+            scratch.sfa_bytes = need;
+        }
         e = sf_tile_launch(a_sf, M, K, BM, scratch.sfa_tiled, s, 2);
         *launches += 1;
         if (e != cudaSuccess) { err = std::string("scale-factor tiling failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     }
 
-    CUtensorMap map_a, map_b, map_sfa;
-    if (!make_map(&map_a, a_codes, M, K, BM) || !make_map(&map_b, w.codes, N, K, BN) ||
-        !(direct ? make_sf_direct_map(&map_sfa, a_sf, M, K) : make_map(&map_sfa, a_codes, M, K, BM))) {
+    CUtensorMap map_a, map_sfa;
+    if (!make_map(&map_a, a_codes, M, K, BM) || !(direct ? make_sf_direct_map(&map_sfa, a_sf, M, K) : make_map(&map_sfa, a_codes, M, K, BM))) {
         err = "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, K a multiple of 32)";
         return MPQ_ERR_CUDA;
     }
-    if (kind == "pair") {
-        const int nclusters = pair_v2_clusters(sm_count);
-        if (nclusters > 0) {
-            CUtensorMap map_bh;
-            if (!make_map(&map_bh, w.codes, N, K, BN / 2)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
-            PairParams pp;
-            pp.C = reinterpret_cast<__nv_bfloat16*>(c);
-            pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
-            pp.m_pairs = (int)((M + 2 * BM - 1) / (2 * BM)); pp.n_tiles = (int)((N + BN - 1) / BN);
-            pp.k_blocks = (int)((K + BK - 1) / BK); pp.ksteps_pad = ksteps_padded(K);
-            pp.scale = ta * w.tensor_scale;
-            pp.status = scratch.status;
-            pp.sfa_direct = direct ? 1 : 0;
-            int grid = 2 * std::min(nclusters, pp.m_pairs * pp.n_tiles);
-            nvfp4_gemm_pair_kernel_v2<<<grid, V2_THREADS, Q_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, pp, scratch.sfa_tiled, w.sf_tiled);
-            *launches += 1;
-            e = cudaGetLastError();
-            if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
-            return MPQ_OK;
-        }
-    }
-    const int clusters = kind == "pair_cp" ? pair_clusters(sm_count) : 0;
-    if (clusters > 0) {
-        // CTA-pair kernel: B is loaded in halves of 112 rows, the scale-factor slabs through tensor maps too
-        CUtensorMap map_bh, map_sfa, map_sfb;
-        const int kp = ksteps_padded(K);
-        const int64_t m_tiles128 = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-        if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_sf_map(&map_sfa, scratch.sfa_tiled, m_tiles128 * kp, 4) ||
-            !make_sf_map(&map_sfb, w.sf_tiled, n_tiles * kp * 2, 8)) {
-            err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel";
-            return MPQ_ERR_CUDA;
-        }
+    // CTA pairs where clusters of two can be scheduled (MPQ_FP4_KERNEL=single forces the one-CTA kernel, which the
+    // parity tests use to cover both)
+    const char* env = getenv("MPQ_FP4_KERNEL");
+    const int nclusters = (env && std::string(env) == "single") ? 0 : pair_v2_clusters(sm_count);
+    if (nclusters > 0) {
+        CUtensorMap map_bh;
+        if (!make_map(&map_bh, w.codes, N, K, BN / 2)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
         PairParams pp;
         pp.C = reinterpret_cast<__nv_bfloat16*>(c);
         pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
-        pp.m_pairs = (int)((M + 2 * BM - 1) / (2 * BM)); pp.n_tiles = (int)n_tiles;
-        pp.k_blocks = (int)((K + BK - 1) / BK); pp.ksteps_pad = kp;
+        pp.m_pairs = (int)((M + 2 * BM - 1) / (2 * BM)); pp.n_tiles = (int)((N + BN - 1) / BN);
+        pp.k_blocks = (int)((K + BK - 1) / BK); pp.ksteps_pad = ksteps_padded(K);
         pp.scale = ta * w.tensor_scale;
         pp.status = scratch.status;
-        int grid = 2 * std::min(clusters, pp.m_pairs * pp.n_tiles);
-        nvfp4_gemm_pair_kernel<<<grid, THREADS, P_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, map_sfb, pp);
+        pp.sfa_direct = direct ? 1 : 0;
+        int grid = 2 * std::min(nclusters, pp.m_pairs * pp.n_tiles);
+        nvfp4_gemm_pair_kernel_v2<<<grid, V2_THREADS, Q_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, pp, scratch.sfa_tiled, w.sf_tiled);
         *launches += 1;
         e = cudaGetLastError();
-        if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+        if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
         return MPQ_OK;
     }
+    CUtensorMap map_b;
+    if (!make_map(&map_b, w.codes, N, K, BN)) { err = "cuTensorMapEncodeTiled failed"; return MPQ_ERR_CUDA; }
     GemmParams p;
     p.sfa = scratch.sfa_tiled; p.sfb = w.sf_tiled; p.C = reinterpret_cast<__nv_bfloat16*>(c);
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
@@ -1342,17 +933,15 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     p.sfa_direct = direct ? 1 : 0;
     static bool configured = false;
     if (!configured) {
-        e = cudaFuncSetAttribute(nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(nvfp4_gemm_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        e = cudaFuncSetAttribute(nvfp4_gemm_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
         configured = true;
     }
     int grid = std::min(sm_count, p.m_tiles * p.n_tiles);
-    if (kind == "single_cp") nvfp4_gemm_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);       // scale factors by tcgen05.cp, two accumulators
-    else nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, p);
+    nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, p);
     *launches += 1;
     e = cudaGetLastError();
-    if (e != cudaSuccess) { err = std::string("nvfp4_gemm_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    if (e != cudaSuccess) { err = std::string("nvfp4_gemm_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     return MPQ_OK;
 }
 
