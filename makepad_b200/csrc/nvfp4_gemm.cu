@@ -565,6 +565,15 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar & 0xFEFFFFFFu) : "memory");
 }
+// TMA tile store shared -> global (rows and columns beyond the tensor are clipped); completion is tracked per thread
+// by bulk groups
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -602,21 +611,25 @@ struct PairParams {
 // writer warps wait for; the writers of both CTAs then arrive on the leader's sf_ready barrier.  One TMEM
 // scale-factor buffer per pipeline stage: a CTA refills a stage only after the leader's commit for the stage's
 // previous use has reached it, so the buffer is free whenever its scale factors arrive.
-constexpr int Q_STAGES = 6;
+constexpr int Q_STAGES = 5;
 constexpr int Q_STAGE_BYTES = A_BYTES + P_BH_BYTES + SFA_BYTES + SFB_BYTES;     // 36864
-constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
+constexpr int Q_OUT_COLS = 56;                                                  // columns per TMA store of one epilogue warp
+constexpr int Q_OUT_BYTES = 32 * Q_OUT_COLS * 2;                                // 3584: 32 rows of bf16, dense
+constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 8 * Q_OUT_BYTES + 1024 + 256;
+static_assert(V2_EPI_COLS % Q_OUT_COLS == 0 && (Q_OUT_COLS * 2) % 16 == 0, "store boxes tile the epilogue columns in 16-byte units");
 static_assert(V2_SF_COL + Q_STAGES * V2_SF_COLS <= TMEM_COLS, "scale-factor buffers must fit beside the accumulator");
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(V2_THREADS, 1)
 nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          const __grid_constant__ CUtensorMap map_sfa, const PairParams p, const uint8_t* __restrict__ sfa,
-                          const uint8_t* __restrict__ sfb)
+                          const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_c, const PairParams p,
+                          const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb)
 {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
     const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t bars = smem0 + Q_STAGES * Q_STAGE_BYTES;
+    const uint32_t out0 = smem0 + Q_STAGES * Q_STAGE_BYTES;          // the epilogue warps' staging tiles
+    const uint32_t bars = out0 + 8 * Q_OUT_BYTES;
     // full: A and B of both CTAs (leader's is used); sf_full: this CTA's scale slabs; empty: commit + 4 local writers;
     // sf_ready: 8 writer warps of the pair (leader's is used)
     const uint32_t bar_full = bars, bar_sf_full = bars + 8 * Q_STAGES, bar_empty = bars + 16 * Q_STAGES,
@@ -688,7 +701,8 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                 tc_fence_after();
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!seen) {
-                        ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT) && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
+                        ok = bar_spin(bar_sf_ready + 8 * stage, phase, SPIN_LIMIT);
+                        ok = ok && bar_spin(bar_full + 8 * stage, phase, SPIN_LIMIT);
                         if (!ok) { atomicExch(p.status, 15); s_abort = 1; break; }
                         tc_fence_after();
                     }
@@ -768,23 +782,33 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                 if (rank == 0) bar_arrive(bar_acc_empty);
                 else bar_arrive_cluster_relaxed(leader_acc_empty);
             }
-            const int row = (2 * mp + (int)rank) * BM + quarter * 32 + lane;
-            if (row < p.M) {
-                const int col0 = nt * BN + half * V2_EPI_COLS;
-                __nv_bfloat16* crow = p.C + (size_t)row * p.N + col0;
+            // Stores: one lane per row would touch 32 rows with every instruction, and all CTAs store at the same time
+            // (the tile boundaries coincide): measured, that stalls the next tile's loads for 2-3 us.  So the tile goes
+            // through shared memory and leaves as TMA tile stores of 32 rows x 56 columns.
+            const int row0 = (2 * mp + (int)rank) * BM + quarter * 32;
+            const int col0 = nt * BN + half * V2_EPI_COLS;
+            const uint32_t stg = out0 + (uint32_t)(warp - 2) * Q_OUT_BYTES;
 #pragma unroll
-                for (int v = 0; v < V2_EPI_COLS / 8; ++v) {
-                    uint4 o;
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
-                    o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                    o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                    if (col0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + 8 * v) = o;
+            for (int round = 0; round < V2_EPI_COLS / Q_OUT_COLS; ++round) {
+                if (lane == 0) tma_store_wait_read();              // the previous store has read the staging tile
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < Q_OUT_COLS / 8; ++v) {
+                    const uint32_t* q = &r[round * Q_OUT_COLS + 8 * v];
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(q[0]) * p.scale, __uint_as_float(q[1]) * p.scale);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(q[2]) * p.scale, __uint_as_float(q[3]) * p.scale);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(q[4]) * p.scale, __uint_as_float(q[5]) * p.scale);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(q[6]) * p.scale, __uint_as_float(q[7]) * p.scale);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * (Q_OUT_COLS * 2) + v * 16),
+                                 "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                                 "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> visible to the TMA engine
+                __syncwarp();
+                if (lane == 0 && row0 < p.M && col0 + round * Q_OUT_COLS < p.N) tma_store_2d(&map_c, col0 + round * Q_OUT_COLS, row0, stg);
             }
         }
+        if (lane == 0) tma_store_wait_all();                       // the stores are complete before the CTA exits
     }
     tc_fence_before();
     __syncthreads();
@@ -840,6 +864,19 @@ static bool make_sf_direct_map(CUtensorMap* map, const void* base, int64_t rows,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+
+// C[M][N] bf16; box = 32 rows x 56 columns, dense
+static bool make_c_map(CUtensorMap* map, void* base, int64_t M, int64_t N)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)N * 2};
+    cuuint32_t box[2] = {(cuuint32_t)Q_OUT_COLS, 32u};
+    cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 // CTA pairs the device can keep resident at once (0: the pair kernel cannot be used)
 
@@ -904,8 +941,8 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     const char* env = getenv("MPQ_FP4_KERNEL");
     const int nclusters = (env && std::string(env) == "single") ? 0 : pair_v2_clusters(sm_count);
     if (nclusters > 0) {
-        CUtensorMap map_bh;
-        if (!make_map(&map_bh, w.codes, N, K, BN / 2)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
+        CUtensorMap map_bh, map_c;
+        if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_c_map(&map_c, c, M, N)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
         PairParams pp;
         pp.C = reinterpret_cast<__nv_bfloat16*>(c);
         pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
@@ -915,7 +952,7 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
         pp.status = scratch.status;
         pp.sfa_direct = direct ? 1 : 0;
         int grid = 2 * std::min(nclusters, pp.m_pairs * pp.n_tiles);
-        nvfp4_gemm_pair_kernel_v2<<<grid, V2_THREADS, Q_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, pp, scratch.sfa_tiled, w.sf_tiled);
+        nvfp4_gemm_pair_kernel_v2<<<grid, V2_THREADS, Q_SMEM_BYTES, s>>>(map_a, map_bh, map_sfa, map_c, pp, scratch.sfa_tiled, w.sf_tiled);
         *launches += 1;
         e = cudaGetLastError();
         if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
