@@ -304,6 +304,9 @@ def main():
         ms, e2e_ms = t.tolist()
         e2e_s = e2e_ms / 1e3
     ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
 
