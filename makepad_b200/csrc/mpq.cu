@@ -40,6 +40,7 @@ struct mpq_context {
     int q4_group;             // chunks per bulk copy of the streaming kernel (2 or 4)
     bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
     int q4_depth;             // most ring stages per warp
+    int q4_pre;               // stages copied before the dependency resolves
     bool q4_slab4;            // M > 4 as slabs of four rows through the streaming kernel
     Nvfp4Scratch fp4;
 };
@@ -140,6 +141,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_group = (e && e[0] == '4') ? 4 : 2;
     e = getenv("MPQ_Q4_DEPTH");
     c->q4_depth = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    e = getenv("MPQ_Q4_PRE");
+    c->q4_pre = (e && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : 1;
     e = getenv("MPQ_Q4_SLAB4");
     c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
@@ -466,7 +469,7 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
         p.tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
         p.nrp = q.nrp;
         p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
-        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
+        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth; p.pre = ctx->q4_pre;
         p.partials = ctx->q4_partials; p.status = ctx->q4_status;
         p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
         for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
@@ -651,7 +654,7 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
             return fail(ctx, MPQ_ERR_UNSUPPORTED, "this launch needs %d scratch slots, the static array holds %d", grid, Q4_STATIC_MAX_CTAS);
         Q4StreamLaunch p;
         p.stream = q.stream; p.X = x; p.Y = y; p.M = m; p.N = (int)q.N; p.K = (int)q.K; p.ldy = q.N;
-        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth;
+        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth; p.pre = ctx->q4_pre;
         p.tile_mode = tile_mode; p.nrp = q.nrp;
         p.partials = reinterpret_cast<uint2*>(base + 256);
         p.status = status_dev ? status_dev : reinterpret_cast<int*>(base);

@@ -465,6 +465,7 @@ struct Q4StreamLaunch {
     int tile_mode;          // 1: CTA b owns row pair-tiles [b*nrp/grid, (b+1)*nrp/grid) and its warps split them
     int nrp;                // row pair-tiles
     int depth;              // ring stages per warp
+    int pre;                // stages copied before the dependency on the previous kernel resolves (the rest after the activation loads)
     uint2* partials;        // [CTAs][2][32 lanes][4] (value, tag) pairs
     int* status;            // set non-zero when a bounded wait ran out
     // row-parallel mode (xworld > 0): finished tiles are not written to Y but pushed, as (value, 1) pairs,
@@ -721,14 +722,18 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
     __syncwarp();
     int issued = 0;
     const uint64_t l2pol = l2_evict_first_policy();
-    if (lane == 0) {
-        const int first = min(D, ngroups);
-        for (; issued < first; ++issued) {
-            mbar_expect_tx(bars_u32 + issued * 8, STAGE_BYTES);
-            bulk_g2s(ring_u32 + issued * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + issued * 8, l2pol);
-            gnext += STAGE_BYTES;
+    // Copies issued here are in flight when the dependency resolves, and the activation loads queue behind them:
+    // only p.pre stages go out now, the rest of the ring right after the activation loads have been issued.
+    auto issue_upto = [&](int n) {
+        if (lane == 0) {
+            for (; issued < n; ++issued) {
+                mbar_expect_tx(bars_u32 + issued * 8, STAGE_BYTES);
+                bulk_g2s(ring_u32 + issued * STAGE_BYTES, gnext, STAGE_BYTES, bars_u32 + issued * 8, l2pol);
+                gnext += STAGE_BYTES;
+            }
         }
-    }
+    };
+    issue_upto(min(min(D, p.pre), ngroups));
 
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -746,6 +751,7 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             xv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (i < total4 && 4 * f < p.K) xv[it] = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
         }
+        issue_upto(min(D, ngroups));
 #pragma unroll
         for (int it = 0; it < NX; ++it) {
             mx = max(mx, __float_as_uint(xv[it].x) & 0x7FFFFFFFu);
@@ -754,6 +760,7 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             mx = max(mx, __float_as_uint(xv[it].w) & 0x7FFFFFFFu);
         }
     } else {
+        issue_upto(min(D, ngroups));
         for (int i = tid; i < total4; i += Q4S_THREADS) {
             int m = i / pk4, f = i - m * pk4;
             if (4 * f < p.K) {
