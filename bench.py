@@ -211,7 +211,7 @@ def extras(ctx, peak):
     ts.sort()
     us = ts[len(ts) // 2]
     out["nvfp4_gemm_2048x4096x14336"] = {"us": us, "tflops": 2.0 * M * N * K / us / 1e6, "frac_of_nominal_dense_fp4_9pf": 2.0 * M * N * K / us / 1e6 / 9000.0,
-                                         "note": "includes re-tiling the activation scale factors; L2 flushed between launches"}
+                                         "note": "one mpq_nvfp4_gemm_forward call; L2 flushed between launches"}
     w.destroy()
     return out
 
