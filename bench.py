@@ -304,6 +304,37 @@ def main():
         ms, e2e_ms = t.tolist()
         e2e_s = e2e_ms / 1e3
     ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+    import types
+    stack_facts = types.SimpleNamespace(launches_per_step=stack.launches_per_step, bytes_per_step=stack.bytes_per_step,
+                                        kernel_name=stack.kernel_name, h2d_bytes_per_step=stack.h2d_bytes_per_step,
+                                        d2h_bytes_per_step=stack.d2h_bytes_per_step)
+    tp_extra = None
+    if dist is not None and not args.no_extra:
+        # configuration 4: the 70B-shape FFN layer tensor-parallel over the same ranks, M = 1; enough copies of the
+        # layer that each rank's weights exceed L2
+        stack.destroy() if hasattr(stack, "destroy") else None
+        del stack
+        torch.cuda.empty_cache()
+        from makepad_b200.decode_stack import q4_bytes as _qb
+        per_rank = sum(_qb(N, K, 1) for (_, N, K, _) in TpDecodeStack.LAYOUT_70B_FFN) / world
+        copies = max(2, int(400e6 // per_rank) + 1)
+        ffn = TpDecodeStack(ctx, rank, world, layers=copies, M=1, seed=11, layout=TpDecodeStack.LAYOUT_70B_FFN).capture()
+        for _ in range(3):
+            ffn.step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(ffn.stream):
+            f0.record()
+            for _ in range(20):
+                ffn.step()
+            f1.record()
+        barrier()
+        t = torch.tensor([f0.elapsed_time(f1)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_ffn = float(t.item()) * 1e3 / 20 / copies
+        tp_extra = {"us_per_ffn": us_ffn, "gbs_whole_job": ffn.bytes_per_step / copies / us_ffn / 1e3, "copies": copies, "n_gpus": world}
+        ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+        stack = None
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -313,6 +344,8 @@ def main():
     ms_per_step = ms / args.steps
     toks = 1e3 / ms_per_step
     peak, peak_src = measured_peak()
+    if stack is None:
+        stack = stack_facts
     launches = stack.launches_per_step
     bytes_per_launch = stack.bytes_per_step / launches / max(1, world) if world > 1 else stack.bytes_per_step / launches
     achieved = stack.bytes_per_step / max(1, world) / (ms_per_step * 1e-3) / 1e9      # per GPU
@@ -331,6 +364,8 @@ def main():
         "gpu_launches": launches * args.steps,
         "clocks": clocks,
     }
+    if tp_extra is not None:
+        out["extra"] = {"q4_70b_ffn_m1_tp": tp_extra}
     if world == 1 and not args.no_extra:
         stack.destroy()
         del stack

@@ -87,7 +87,9 @@ constexpr int B_BYTES = BN * BK / 2;                       // 28672
 constexpr int SFA_BYTES = 4 * 512;                         // four K steps x one 128-row atom
 constexpr int SFB_BYTES = 4 * 2 * 512;                     // four K steps x two atoms (224 rows)
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;   // 51200
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int OUT_COLS = 16;                               // columns per TMA store of one epilogue warp (one-CTA kernel)
+constexpr int OUT_BYTES = 32 * OUT_COLS * 2;               // 1024: 32 rows of bf16, dense
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 8 * OUT_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;     // polls of one mbarrier before the kernel gives up and reports it
 
@@ -257,6 +259,15 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r)
                    "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// TMA tile store shared -> global (rows and columns beyond the tensor are clipped); completion is tracked per thread
+// by bulk groups
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ bool bar_test(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -352,13 +363,14 @@ __device__ __forceinline__ void load_sf_registers(const unsigned char* src, bool
 
 __global__ void __launch_bounds__(V2_THREADS, 1)
 nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                     const __grid_constant__ CUtensorMap map_sfa, const GemmParams p)
+                     const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_c, const GemmParams p)
 {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile int s_abort;
     const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
-    const uint32_t bars = smem0 + STAGES * STAGE_BYTES;
+    const uint32_t out0 = smem0 + STAGES * STAGE_BYTES;              // the epilogue warps' staging tiles
+    const uint32_t bars = out0 + 8 * OUT_BYTES;
     const uint32_t bar_full = bars, bar_empty = bars + 8 * STAGES, bar_sf_ready = bars + 16 * STAGES,
                    bar_acc_full = bars + 24 * STAGES, bar_acc_empty = bars + 24 * STAGES + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -500,23 +512,31 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) bar_arrive(bar_acc_empty);          // the next tile's MMAs may overwrite the accumulator
-            const int row = mt * BM + quarter * 32 + lane;
-            if (row < p.M) {
-                const int col0 = nt * BN + half * V2_EPI_COLS;
-                __nv_bfloat16* crow = p.C + (size_t)row * p.N + col0;
+            // the tile leaves through shared memory as TMA tile stores of 32 rows x 16 columns (see the pair kernel)
+            const int row0 = mt * BM + quarter * 32;
+            const int col0 = nt * BN + half * V2_EPI_COLS;
+            const uint32_t stg = out0 + (uint32_t)(warp - 2) * OUT_BYTES;
 #pragma unroll
-                for (int v = 0; v < V2_EPI_COLS / 8; ++v) {
-                    uint4 o;
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 0]) * p.scale, __uint_as_float(r[8 * v + 1]) * p.scale);
-                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 2]) * p.scale, __uint_as_float(r[8 * v + 3]) * p.scale);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 4]) * p.scale, __uint_as_float(r[8 * v + 5]) * p.scale);
-                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[8 * v + 6]) * p.scale, __uint_as_float(r[8 * v + 7]) * p.scale);
-                    o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                    o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                    if (col0 + 8 * v + 8 <= p.N) *reinterpret_cast<uint4*>(crow + 8 * v) = o;
+            for (int round = 0; round < V2_EPI_COLS / OUT_COLS; ++round) {
+                if (lane == 0) tma_store_wait_read();              // the previous store has read the staging tile
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < OUT_COLS / 8; ++v) {
+                    const uint32_t* q = &r[round * OUT_COLS + 8 * v];
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(q[0]) * p.scale, __uint_as_float(q[1]) * p.scale);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(q[2]) * p.scale, __uint_as_float(q[3]) * p.scale);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(q[4]) * p.scale, __uint_as_float(q[5]) * p.scale);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(q[6]) * p.scale, __uint_as_float(q[7]) * p.scale);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * (OUT_COLS * 2) + v * 16),
+                                 "r"(*reinterpret_cast<uint32_t*>(&h0)), "r"(*reinterpret_cast<uint32_t*>(&h1)),
+                                 "r"(*reinterpret_cast<uint32_t*>(&h2)), "r"(*reinterpret_cast<uint32_t*>(&h3)) : "memory");
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> visible to the TMA engine
+                __syncwarp();
+                if (lane == 0 && row0 < p.M && col0 + round * OUT_COLS < p.N) tma_store_2d(&map_c, col0 + round * OUT_COLS, row0, stg);
             }
         }
+        if (lane == 0) tma_store_wait_all();                       // the stores are complete before the CTA exits
     }
     tc_fence_before();
     __syncthreads();
@@ -565,15 +585,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar & 0xFEFFFFFFu) : "memory");
 }
-// TMA tile store shared -> global (rows and columns beyond the tensor are clipped); completion is tracked per thread
-// by bulk groups
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, uint32_t src)
-{
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -865,14 +876,14 @@ static bool make_sf_direct_map(CUtensorMap* map, const void* base, int64_t rows,
 }
 
 
-// C[M][N] bf16; box = 32 rows x 56 columns, dense
-static bool make_c_map(CUtensorMap* map, void* base, int64_t M, int64_t N)
+// C[M][N] bf16; box = 32 rows x box_cols columns, dense
+static bool make_c_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int box_cols)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
     cuuint64_t strides[1] = {(cuuint64_t)N * 2};
-    cuuint32_t box[2] = {(cuuint32_t)Q_OUT_COLS, 32u};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, 32u};
     cuuint32_t estr[2] = {1u, 1u};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -942,7 +953,7 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     const int nclusters = (env && std::string(env) == "single") ? 0 : pair_v2_clusters(sm_count);
     if (nclusters > 0) {
         CUtensorMap map_bh, map_c;
-        if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_c_map(&map_c, c, M, N)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
+        if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_c_map(&map_c, c, M, N, Q_OUT_COLS)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
         PairParams pp;
         pp.C = reinterpret_cast<__nv_bfloat16*>(c);
         pp.M = (int)M; pp.N = (int)N; pp.K = (int)K;
@@ -958,8 +969,8 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
         if (e != cudaSuccess) { err = std::string("nvfp4_gemm_pair_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
         return MPQ_OK;
     }
-    CUtensorMap map_b;
-    if (!make_map(&map_b, w.codes, N, K, BN)) { err = "cuTensorMapEncodeTiled failed"; return MPQ_ERR_CUDA; }
+    CUtensorMap map_b, map_c1;
+    if (!make_map(&map_b, w.codes, N, K, BN) || !make_c_map(&map_c1, c, M, N, OUT_COLS)) { err = "cuTensorMapEncodeTiled failed"; return MPQ_ERR_CUDA; }
     GemmParams p;
     p.sfa = scratch.sfa_tiled; p.sfb = w.sf_tiled; p.C = reinterpret_cast<__nv_bfloat16*>(c);
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
@@ -975,7 +986,7 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
         configured = true;
     }
     int grid = std::min(sm_count, p.m_tiles * p.n_tiles);
-    nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, p);
+    nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, map_c1, p);
     *launches += 1;
     e = cudaGetLastError();
     if (e != cudaSuccess) { err = std::string("nvfp4_gemm_kernel_v2 launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }

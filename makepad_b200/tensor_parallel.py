@@ -137,19 +137,25 @@ class TpDecodeStack:
     # (name, N, K, mode)
     LAYOUT = (("qkv", 12288, 4096, _lib.TP_COLUMN), ("o", 4096, 4096, _lib.TP_ROW),
               ("gate_up", 22016, 4096, _lib.TP_COLUMN), ("down", 4096, 11008, _lib.TP_ROW))
+    # the 70B-shape FFN: gate+up 8192 -> 2 x 28672 column-split, down 28672 -> 8192 row-split + sum over ranks
+    LAYOUT_70B_FFN = (("gate_up", 57344, 8192, _lib.TP_COLUMN), ("down", 8192, 28672, _lib.TP_ROW))
 
-    def __init__(self, ctx: Context, rank: int, world: int, layers: int = 32, M: int = 1, seed: int = 0, fused: bool = True):
+    def __init__(self, ctx: Context, rank: int, world: int, layers: int = 32, M: int = 1, seed: int = 0, fused: bool = True,
+                 layout=None):
         import torch
         self.ctx, self.rank, self.world, self.layers, self.M, self.fused = ctx, rank, world, layers, M, fused
+        if layout is not None:
+            self.LAYOUT = tuple(layout)
         self.dev = torch.device(f"cuda:{ctx.device}")
-        self.ex = Exchange(ctx, rank, world, max_floats=M * 4096) if fused else None
+        row_n = max([N for (_, N, _, mode) in self.LAYOUT if mode == _lib.TP_ROW] + [1])
+        self.ex = Exchange(ctx, rank, world, max_floats=M * row_n) if fused else None
         self.weights, self.modes = [], []
         for layer in range(layers):
             for j, (_, N, K, mode) in enumerate(self.LAYOUT):
                 n, k = (N // world, K) if mode == _lib.TP_COLUMN else (N, K // world)
                 if mode == _lib.TP_ROW and (K // world) % 32:
                     raise ValueError(f"K={K} does not split into {world} multiples of 32")
-                self.weights.append(random_q4_weight_on_device(ctx, n, k, seed + 1000 * rank + layer * 4 + j))
+                self.weights.append(random_q4_weight_on_device(ctx, n, k, seed + 1000 * rank + layer * len(self.LAYOUT) + j))
                 self.modes.append(mode)
         self.x_off, self.y_off, xo, yo = [], [], 0, 0
         for w in self.weights:
@@ -221,3 +227,15 @@ class TpDecodeStack:
     @property
     def d2h_bytes_per_step(self) -> int:
         return self.y_last_host.numel() * 4
+
+    def destroy(self):
+        """Free the graph, the weights and the exchange (every rank calls it at the same point)."""
+        import torch
+        torch.cuda.synchronize()
+        self.graph = None
+        for w in self.weights:
+            w.destroy()
+        self.weights = []
+        if self.ex is not None:
+            self.ex.destroy()
+            self.ex = None
