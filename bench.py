@@ -318,6 +318,7 @@ def main():
         from makepad_b200.decode_stack import q4_bytes as _qb
         per_rank = sum(_qb(N, K, 1) for (_, N, K, _) in TpDecodeStack.LAYOUT_70B_FFN) / world
         copies = max(2, int(400e6 // per_rank) + 1)
+        copies += copies & 1                 # a replayed graph must hold an even number of calls per exchange
         ffn = TpDecodeStack(ctx, rank, world, layers=copies, M=1, seed=11, layout=TpDecodeStack.LAYOUT_70B_FFN).capture()
         for _ in range(3):
             ffn.step()
