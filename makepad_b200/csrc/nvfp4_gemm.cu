@@ -429,6 +429,9 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
             uint32_t phase = 0;
             bool seen = false;                         // the barriers of (stage, phase) have already been observed
             bool ok = true;
+            const uint64_t adesc0 = smem_desc_sw128(smem0), bdesc0 = smem_desc_sw128(smem0 + A_BYTES);
+            const uint32_t sfc0 = tmem + V2_SF_COL;
+            uint32_t soff = 0, sfoff = 0;              // stage * (STAGE_BYTES >> 4), stage * V2_SF_COLS
             for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
                 // the accumulator is free once the eight epilogue warps hold the previous tile in registers
                 if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 4); s_abort = 1; break; }
@@ -440,23 +443,29 @@ nvfp4_gemm_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __grid_con
                         tc_fence_after();
                     }
                     seen = false;
-                    const uint32_t st = smem0 + stage * STAGE_BYTES;
-                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
-                    const uint32_t sfb_t = tmem + V2_SF_COL + stage * V2_SF_COLS, sfa_t = sfb_t + 32;
-#pragma unroll
-                    for (int ks = 0; ks < 3; ++ks)         // +32 bytes along K inside the swizzle atom = +2 in the address field
-                        tc_mma_nvf4(tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, sfa_t + ks * 4, sfb_t + ks * 8, (kb | ks) ? 1u : 0u);
-                    // while those run: is the next K block (of this tile or the next one) ready?
+                    // Whatever runs between two MMAs must be shorter than one MMA (112 cycles) or the pipe idles: the look at
+                    // the next K block's two barriers and the fence are spread over the gaps, the address arithmetic is a few adds.
+                    const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+                    const uint32_t sfb_c = sfc0 + sfoff, sfa_c = sfb_c + 32;
                     ++done_kb;
                     int nstage = stage + 1;
                     uint32_t nphase = phase;
                     if (nstage == STAGES) { nstage = 0; nphase ^= 1u; }
-                    if (done_kb < total_kb && bar_test(bar_sf_ready + 8 * nstage, nphase) && bar_test(bar_full + 8 * nstage, nphase)) {
-                        tc_fence_after();                  // seen now, while MMAs are queued; if not ready, the last MMA and
-                        seen = true;                       // the commit that frees this stage must not wait for it
+                    const bool more = done_kb < total_kb;
+                    tc_mma_nvf4(tmem, adesc, bdesc, idesc, sfa_c, sfb_c, kb ? 1u : 0u);
+                    const bool r1 = more && bar_test(bar_sf_ready + 8 * nstage, nphase);
+                    tc_mma_nvf4(tmem, adesc + 2, bdesc + 2, idesc, sfa_c + 4, sfb_c + 8, 1u);        // +32 bytes along K = +2
+                    const bool r2 = r1 && bar_test(bar_full + 8 * nstage, nphase);
+                    tc_mma_nvf4(tmem, adesc + 4, bdesc + 4, idesc, sfa_c + 8, sfb_c + 16, 1u);
+                    if (r2) {
+                        tc_fence_after();                  // seen now; if not ready, the last MMA and the commit that frees this
+                        seen = true;                       // stage must not wait for it
                     }
-                    tc_mma_nvf4(tmem, adesc + 6, bdesc + 6, idesc, sfa_t + 12, sfb_t + 24, 1u);
-                    tc_commit(bar_empty + 8 * stage);      // the stage and its scale-factor buffer are free when these MMAs are done
+                    tc_mma_nvf4(tmem, adesc + 6, bdesc + 6, idesc, sfa_c + 12, sfb_c + 24, 1u);
+                    tc_commit(bar_empty + 8 * stage);       // the stage and its scale-factor buffer are free when these MMAs are done
+                    soff += STAGE_BYTES >> 4;
+                    sfoff += V2_SF_COLS;
+                    if (nstage == 0) { soff = 0; sfoff = 0; }
                     stage = nstage;
                     phase = nphase;
                 }
@@ -707,6 +716,9 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
             int stage = 0;
             uint32_t phase = 0;
             bool seen = false, ok = true;
+            const uint64_t adesc0 = smem_desc_sw128(smem0), bdesc0 = smem_desc_sw128(smem0 + A_BYTES);
+            const uint32_t sfc0 = tmem + V2_SF_COL;
+            uint32_t soff = 0, sfoff = 0;              // stage * (Q_STAGE_BYTES >> 4), stage * V2_SF_COLS
             for (int local = 0; local < my_tiles && ok && !s_abort; ++local) {
                 if (local > 0 && !bar_spin(bar_acc_empty, (uint32_t)(local - 1) & 1u, SPIN_LIMIT)) { atomicExch(p.status, 14); s_abort = 1; break; }
                 tc_fence_after();
@@ -718,22 +730,29 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
                         tc_fence_after();
                     }
                     seen = false;
-                    const uint32_t st = smem0 + stage * Q_STAGE_BYTES;
-                    const uint64_t adesc = smem_desc_sw128(st), bdesc = smem_desc_sw128(st + A_BYTES);
-                    const uint32_t sfb_c = tmem + V2_SF_COL + stage * V2_SF_COLS, sfa_c = sfb_c + 32;
-#pragma unroll
-                    for (int ks = 0; ks < 3; ++ks)
-                        tc_mma_nvf4_pair(tmem, adesc + 2 * ks, bdesc + 2 * ks, idesc, sfa_c + ks * 4, sfb_c + ks * 8, (kb | ks) ? 1u : 0u);
+                    // Whatever runs between two MMAs must be shorter than one MMA (112 cycles) or the pipe idles: the look at
+                    // the next K block's two barriers and the fence are spread over the gaps, the address arithmetic is a few adds.
+                    const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+                    const uint32_t sfb_c = sfc0 + sfoff, sfa_c = sfb_c + 32;
                     ++done_kb;
                     int nstage = stage + 1;
                     uint32_t nphase = phase;
                     if (nstage == Q_STAGES) { nstage = 0; nphase ^= 1u; }
-                    if (done_kb < total_kb && bar_test(bar_sf_ready + 8 * nstage, nphase) && bar_test(bar_full + 8 * nstage, nphase)) {
-                        tc_fence_after();                  // seen now, while MMAs are queued; if not ready, the last MMA and
-                        seen = true;                       // the commit that frees this stage must not wait for it
+                    const bool more = done_kb < total_kb;
+                    tc_mma_nvf4_pair(tmem, adesc, bdesc, idesc, sfa_c, sfb_c, kb ? 1u : 0u);
+                    const bool r1 = more && bar_test(bar_sf_ready + 8 * nstage, nphase);
+                    tc_mma_nvf4_pair(tmem, adesc + 2, bdesc + 2, idesc, sfa_c + 4, sfb_c + 8, 1u);        // +32 bytes along K = +2
+                    const bool r2 = r1 && bar_test(bar_full + 8 * nstage, nphase);
+                    tc_mma_nvf4_pair(tmem, adesc + 4, bdesc + 4, idesc, sfa_c + 8, sfb_c + 16, 1u);
+                    if (r2) {
+                        tc_fence_after();                  // seen now; if not ready, the last MMA and the commit that frees this
+                        seen = true;                       // stage must not wait for it
                     }
                     tc_mma_nvf4_pair(tmem, adesc + 6, bdesc + 6, idesc, sfa_c + 12, sfb_c + 24, 1u);
-                    tc_commit_pair(bar_empty + 8 * stage);       // both CTAs may refill the stage and its scale-factor buffer
+                    tc_commit_pair(bar_empty + 8 * stage);       // the stage and its scale-factor buffer are free when these MMAs are done
+                    soff += Q_STAGE_BYTES >> 4;
+                    sfoff += V2_SF_COLS;
+                    if (nstage == 0) { soff = 0; sfoff = 0; }
                     stage = nstage;
                     phase = nphase;
                 }
