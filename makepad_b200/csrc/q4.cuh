@@ -789,6 +789,7 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
     if (NX > 0) {
 #pragma unroll
         for (int it = 0; it < NX; ++it) {
+            if (it * Q4S_THREADS >= total4) break;             // the same for the whole CTA: nothing left to stage
             int i = it * Q4S_THREADS + tid;
             bool on = i < total4;
             int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
