@@ -526,7 +526,14 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
 }
 
-__device__ __forceinline__ int q4s_run_start(int i, int groups, int W) { return (int)(((int64_t)i * groups) / W); }
+// floor(i * groups / W); 64-bit division costs a hundred-odd instructions, and these run before a CTA's first copy,
+// so the product is divided in 32 bits whenever it fits (it does for every matrix up to a few GB)
+__device__ __forceinline__ int q4s_run_start(int i, int groups, int W)
+{
+    const uint64_t prod = (uint64_t)(uint32_t)i * (uint32_t)groups;
+    if (prod < 0x100000000ull) return (int)((uint32_t)prod / (uint32_t)W);
+    return (int)(prod / (uint64_t)W);
+}
 // index of the warp whose run contains group gidx
 __device__ __forceinline__ int q4s_owner(int gidx, int groups, int W)
 {
@@ -701,10 +708,10 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
     const int gpr = p.nchunks / G;                            // groups per row pair-tile
     int cta_gb, cta_ge, gb, ge;
     if (p.tile_mode) {
-        cta_gb = (int)(((int64_t)blockIdx.x * p.nrp) / gridDim.x) * gpr;
-        cta_ge = (int)(((int64_t)(blockIdx.x + 1) * p.nrp) / gridDim.x) * gpr;
-        gb = cta_gb + (int)(((int64_t)warp * (cta_ge - cta_gb)) / Q4S_WARPS);
-        ge = cta_gb + (int)(((int64_t)(warp + 1) * (cta_ge - cta_gb)) / Q4S_WARPS);
+        cta_gb = q4s_run_start((int)blockIdx.x, p.nrp, (int)gridDim.x) * gpr;
+        cta_ge = q4s_run_start((int)blockIdx.x + 1, p.nrp, (int)gridDim.x) * gpr;
+        gb = cta_gb + q4s_run_start(warp, cta_ge - cta_gb, Q4S_WARPS);
+        ge = cta_gb + q4s_run_start(warp + 1, cta_ge - cta_gb, Q4S_WARPS);
     } else {
         cta_gb = q4s_run_start(min(W, (int)blockIdx.x * Q4S_WARPS), p.groups, W);
         cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * Q4S_WARPS), p.groups, W);
