@@ -177,8 +177,11 @@ int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, m
 /* ---- NVFP4 GEMM ---------------------------------------------------------- */
 /* C[M][N] (bf16 bits, row-major) = bf16( tsA * tsB * sum_k A~[m,k] * B~[n,k] ).
  * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; any
- * M >= 1.  The activation scale factors are re-tiled on the GPU inside this
- * call (counted in its time) into scratch the context owns. */
+ * M >= 1.  When K is a multiple of 256 the kernel reads the activation scale
+ * factors straight from that array; otherwise they are first re-tiled on the
+ * GPU inside this call (counted in its time) into scratch the context owns.
+ * C must not overlap A (it is written with TMA tile stores while other tiles
+ * are still being read). */
 int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
                                const uint8_t* a_codes_dev, const uint8_t* a_sf_dev, float a_tensor_scale,
                                int64_t M, uint16_t* c_bf16_dev, void* stream);
