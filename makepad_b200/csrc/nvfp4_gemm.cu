@@ -631,10 +631,10 @@ struct PairParams {
 // writer warps wait for; the writers of both CTAs then arrive on the leader's sf_ready barrier.  One TMEM
 // scale-factor buffer per pipeline stage: a CTA refills a stage only after the leader's commit for the stage's
 // previous use has reached it, so the buffer is free whenever its scale factors arrive.
-constexpr int Q_STAGES = 5;
+constexpr int Q_STAGES = 6;
 constexpr int Q_STAGE_BYTES = A_BYTES + P_BH_BYTES + SFA_BYTES + SFB_BYTES;     // 36864
-constexpr int Q_OUT_COLS = 56;                                                  // columns per TMA store of one epilogue warp
-constexpr int Q_OUT_BYTES = 32 * Q_OUT_COLS * 2;                                // 3584: 32 rows of bf16, dense
+constexpr int Q_OUT_COLS = 16;                                                  // columns per TMA store of one epilogue warp
+constexpr int Q_OUT_BYTES = 32 * Q_OUT_COLS * 2;                                // 1024: 32 rows of bf16, dense
 constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 8 * Q_OUT_BYTES + 1024 + 256;
 static_assert(V2_EPI_COLS % Q_OUT_COLS == 0 && (Q_OUT_COLS * 2) % 16 == 0, "store boxes tile the epilogue columns in 16-byte units");
 static_assert(V2_SF_COL + Q_STAGES * V2_SF_COLS <= TMEM_COLS, "scale-factor buffers must fit beside the accumulator");
