@@ -814,7 +814,7 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
             }
             // Stores: one lane per row would touch 32 rows with every instruction, and all CTAs store at the same time
             // (the tile boundaries coincide): measured, that stalls the next tile's loads for 2-3 us.  So the tile goes
-            // through shared memory and leaves as TMA tile stores of 32 rows x 56 columns.
+            // through shared memory and leaves as TMA tile stores of 32 rows x Q_OUT_COLS columns.
             const int row0 = (2 * mp + (int)rank) * BM + quarter * 32;
             const int col0 = nt * BN + half * V2_EPI_COLS;
             const uint32_t stg = out0 + (uint32_t)(warp - 2) * Q_OUT_BYTES;
