@@ -34,7 +34,7 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read+write per launch / algorithmic bytes per launch of q4_stream_kernel, from the ncu
 # capture summarised in profiles/q4_stream_kernel_22016x4096_m1.md
-TRAFFIC_OVER_ALGORITHMIC = 1.009
+TRAFFIC_OVER_ALGORITHMIC = 1.007
 Q_CLOCKS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
