@@ -32,8 +32,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read+write per launch / algorithmic bytes per launch of q4_stream_kernel, from the ncu
-# capture summarised in profiles/q4_stream_kernel_22016x4096_m1.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one q4_stream_kernel launch / its algorithmic bytes, from an ncu
+# capture of the 22016 x 4096 projection (the weights are streamed exactly once, evict-first)
 TRAFFIC_OVER_ALGORITHMIC = 1.007
 Q_CLOCKS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -133,6 +133,61 @@ def _time_graph(torch, enqueue, stream, reps):
     return e0.elapsed_time(e1) * 1e3 / reps
 
 
+def _time_stack(torch, st, reps):
+    """us per replay of a captured stack, CUDA events on its stream."""
+    for _ in range(3):
+        st.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(st.stream):
+        e0.record()
+        for _ in range(reps):
+            st.step()
+        e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps
+
+
+def ceilings(ctx):
+    """Measured ceilings: read-only HBM streaming over 4 GiB, and the FP4 tensor pipe issuing MMAs with nothing in its way."""
+    import ctypes as C
+    import torch
+    out = {}
+    n = 4 << 30
+    buf = torch.empty(n, dtype=torch.uint8, device="cuda")
+    buf.random_(0, 256)
+    sink = torch.zeros(4, dtype=torch.int32, device="cuda")
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(2):
+        ctx.check(ctx.lib.mpq_probe_hbm_read(ctx.h, C.c_void_p(buf.data_ptr()), n, C.c_void_p(sink.data_ptr()), s))
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.check(ctx.lib.mpq_probe_hbm_read(ctx.h, C.c_void_p(buf.data_ptr()), n, C.c_void_p(sink.data_ptr()), s))
+        e1.record(); torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    out["hbm_read_only_gbs"] = n / (min(ts) * 1e-3) / 1e9
+    del buf
+    torch.cuda.empty_cache()
+    flop = C.c_double()
+    mmas = 16384
+    for _ in range(2):
+        ctx.check(ctx.lib.mpq_probe_fp4_mma(ctx.h, mmas, C.byref(flop), s))
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.check(ctx.lib.mpq_probe_fp4_mma(ctx.h, mmas, C.byref(flop), s))
+        e1.record(); torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    out["fp4_mma_only_tflops"] = flop.value / (min(ts) * 1e-3) / 1e12
+    out["fp4_mma_only_note"] = f"{mmas} tcgen05.mma kind::mxf4nvf4 128x224x64 per SM, operands resident, best of 5"
+    return out
+
+
 def extras(ctx, peak):
     """The other configurations of the task, measured in the same run (N = 1): single Q4 matvec (config 0),
     small-M verify batches (config 2), NVFP4 prefill GEMM (config 3), the 70B-shape FFN on one GPU (config 4)."""
@@ -140,7 +195,8 @@ def extras(ctx, peak):
     import torch
     import makepad_b200
     from makepad_b200.decode_stack import DecodeStack, SHAPES_70B_FFN, q4_bytes, random_q4_weight_on_device
-    out = {}
+    out = ceilings(ctx)
+    read_peak = out["hbm_read_only_gbs"]
     side = torch.cuda.Stream()
     # config 0: 4096 x 4096, M = 1; 43 distinct copies so that every launch misses L2
     ws = [random_q4_weight_on_device(ctx, 4096, 4096, 1000 + i) for i in range(43)]
@@ -151,51 +207,37 @@ def extras(ctx, peak):
             ctx.check(ctx.lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(x.data_ptr()), 1, C.c_void_p(y.data_ptr()), s))
     us = _time_graph(torch, enq, side, 10) / len(ws)
     b = q4_bytes(4096, 4096, 1)
-    out["q4_matvec_4096x4096_m1"] = {"us": us, "gbs": b / us / 1e3, "frac_of_hbm_peak": b / us / 1e3 / peak}
+    out["q4_matvec_4096x4096_m1"] = {"us": us, "gbs": b / us / 1e3, "frac_of_hbm_peak": b / us / 1e3 / peak,
+                                     "frac_of_read_only_peak": b / us / 1e3 / read_peak, "frac_of_nominal_8tbs": b / us / 1e3 / 8000.0}
     for w in ws:
         w.destroy()
     # config 2: small-M verify batches on the 7B shapes (4 layers of distinct weights = 455 MB > L2)
     small = {}
     for M in (1, 2, 4, 8, 16):
         st = DecodeStack(ctx, layers=4, M=M, seed=7).capture()
-        for _ in range(3):
-            st.step()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(st.stream):
-            e0.record()
-            for _ in range(20):
-                st.step()
-            e1.record()
-        torch.cuda.synchronize()
-        us_layer = e0.elapsed_time(e1) * 1e3 / 20 / 4
-        small[f"M={M}"] = {"us_per_layer": us_layer, "gbs": st.bytes_per_step / 4 / us_layer / 1e3}
+        us_layer = _time_stack(torch, st, 20) / 4
+        small[f"M={M}"] = {"us_per_layer": us_layer, "gbs": st.bytes_per_step / 4 / us_layer / 1e3, "launches_per_layer": st.launches_per_step // 4}
         st.destroy()
     for k in small:
         small[k]["time_vs_m1"] = small[k]["us_per_layer"] / small["M=1"]["us_per_layer"]
     out["q4_small_m_7b_layer"] = small
-    # config 4 on one GPU: 70B-shape FFN, M = 1 (two copies of each weight: 793 MB per pass)
-    st = DecodeStack(ctx, layers=2, M=1, shapes=SHAPES_70B_FFN, seed=9).capture()
-    for _ in range(3):
-        st.step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(st.stream):
-        e0.record()
-        for _ in range(20):
-            st.step()
-        e1.record()
-    torch.cuda.synchronize()
-    us_ffn = e0.elapsed_time(e1) * 1e3 / 20 / 2
-    out["q4_70b_ffn_m1"] = {"us_per_ffn": us_ffn, "gbs": st.bytes_per_step / 2 / us_ffn / 1e3, "frac_of_hbm_peak": st.bytes_per_step / 2 / us_ffn / 1e3 / peak}
-    st.destroy()
+    # config 4 on one GPU: 70B-shape FFN at both batch widths (two copies of each weight: 793 MB per pass)
+    for M in (1, 64):
+        st = DecodeStack(ctx, layers=2, M=M, shapes=SHAPES_70B_FFN, seed=9).capture()
+        us_ffn = _time_stack(torch, st, 20 if M == 1 else 5) / 2
+        gbs = st.bytes_per_step / 2 / us_ffn / 1e3
+        out[f"q4_70b_ffn_m{M}"] = {"us_per_ffn": us_ffn, "gbs": gbs, "frac_of_hbm_peak": gbs / peak, "frac_of_read_only_peak": gbs / read_peak,
+                                   "launches_per_ffn": st.launches_per_step // 2}
+        st.destroy()
+    out["q4_70b_ffn_m64"]["time_vs_m1"] = out["q4_70b_ffn_m64"]["us_per_ffn"] / out["q4_70b_ffn_m1"]["us_per_ffn"]
     # config 3: NVFP4 prefill GEMM 2048 x 4096 x 14336 -> bf16, L2 flushed between launches
     M, N, K = 2048, 14336, 4096
     g = torch.Generator(device="cuda"); g.manual_seed(3)
     a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device="cuda", generator=g)
     bq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
-    sfa = torch.randint(0x10, 0x40, (M, K // 16), dtype=torch.uint8, device="cuda", generator=g)
-    sfb = torch.randint(0x10, 0x40, (N, K // 16), dtype=torch.uint8, device="cuda", generator=g)
+    # scale factors as the configuration states them: e4m3(|N(0,1)| * 0.1)
+    sfa = (torch.randn((M, K // 16), device="cuda", generator=g).abs() * 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
+    sfb = (torch.randn((N, K // 16), device="cuda", generator=g).abs() * 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
     w = makepad_b200.Nvfp4Weight(ctx, bq.cpu().numpy(), sfb.cpu().numpy(), 1.0)
     lin = makepad_b200.QuantLinear(w)
     c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
@@ -210,8 +252,10 @@ def extras(ctx, peak):
         ts.append(e0.elapsed_time(e1) * 1e3)
     ts.sort()
     us = ts[len(ts) // 2]
-    out["nvfp4_gemm_2048x4096x14336"] = {"us": us, "tflops": 2.0 * M * N * K / us / 1e6, "frac_of_nominal_dense_fp4_9pf": 2.0 * M * N * K / us / 1e6 / 9000.0,
-                                         "note": "one mpq_nvfp4_gemm_forward call; L2 flushed between launches"}
+    tf = 2.0 * M * N * K / us / 1e6
+    out["nvfp4_gemm_2048x4096x14336"] = {"us": us, "tflops": tf, "frac_of_nominal_dense_fp4_9pf": tf / 9000.0,
+                                         "frac_of_measured_mma_only": tf / out["fp4_mma_only_tflops"],
+                                         "note": "one mpq_nvfp4_gemm_forward call; L2 flushed between launches; scales e4m3(|N(0,1)|*0.1)"}
     w.destroy()
     return out
 
@@ -262,7 +306,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
         from makepad_b200.tensor_parallel import TpDecodeStack
         ctx = makepad_b200.Context(local_rank)
-        stack = TpDecodeStack(ctx, rank, world).capture()
+        stack = TpDecodeStack(ctx, rank, world, keep_layer0=True).capture()
     else:
         dist = None
         ctx = makepad_b200.Context(local_rank)
@@ -309,32 +353,50 @@ def main():
                                         kernel_name=stack.kernel_name, h2d_bytes_per_step=stack.h2d_bytes_per_step,
                                         d2h_bytes_per_step=stack.d2h_bytes_per_step)
     tp_extra = None
+    if dist is not None:
+        # Correctness evidence for the sharded run, outside every timed region: the first layer's outputs of the stack
+        # just timed against the CPU checker (column slices on every rank, the fused row-parallel sums on rank 0).
+        from oracle import oracle as orc
+        if rank == 0:
+            orc.build()
+        dist.barrier()
+        parity = stack.parity_of_layer0(orc)
+        tp_extra = {"parity": parity}
     if dist is not None and not args.no_extra:
-        # configuration 4: the 70B-shape FFN layer tensor-parallel over the same ranks, M = 1; enough copies of the
-        # layer that each rank's weights exceed L2
-        stack.destroy() if hasattr(stack, "destroy") else None
+        # configuration 4: the 70B-shape FFN layer tensor-parallel over the same ranks, M = 1 and M = 64; enough copies
+        # of the layer that each rank's weights exceed L2
+        stack.destroy()
         del stack
         torch.cuda.empty_cache()
         from makepad_b200.decode_stack import q4_bytes as _qb
         per_rank = sum(_qb(N, K, 1) for (_, N, K, _) in TpDecodeStack.LAYOUT_70B_FFN) / world
         copies = max(2, int(400e6 // per_rank) + 1)
         copies += copies & 1                 # a replayed graph must hold an even number of calls per exchange
-        ffn = TpDecodeStack(ctx, rank, world, layers=copies, M=1, seed=11, layout=TpDecodeStack.LAYOUT_70B_FFN).capture()
-        for _ in range(3):
-            ffn.step()
-        barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(ffn.stream):
-            f0.record()
-            for _ in range(20):
+        for Mb in (1, 64):
+            ffn = TpDecodeStack(ctx, rank, world, layers=copies, M=Mb, seed=11, layout=TpDecodeStack.LAYOUT_70B_FFN,
+                                keep_layer0=True).capture()
+            for _ in range(3):
                 ffn.step()
-            f1.record()
-        barrier()
-        t = torch.tensor([f0.elapsed_time(f1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us_ffn = float(t.item()) * 1e3 / 20 / copies
-        tp_extra = {"us_per_ffn": us_ffn, "gbs_whole_job": ffn.bytes_per_step / copies / us_ffn / 1e3, "copies": copies, "n_gpus": world}
-        ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+            barrier()
+            reps = 20 if Mb == 1 else 5
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(ffn.stream):
+                f0.record()
+                for _ in range(reps):
+                    ffn.step()
+                f1.record()
+            barrier()
+            t = torch.tensor([f0.elapsed_time(f1)], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us_ffn = float(t.item()) * 1e3 / reps / copies
+            par = ffn.parity_of_layer0(orc)
+            tp_extra[f"q4_70b_ffn_m{Mb}_tp"] = {"us_per_ffn": us_ffn, "gbs_whole_job": ffn.bytes_per_step / copies / us_ffn / 1e3, "copies": copies,
+                                                 "n_gpus": world, "row_parallel_sum": "in-kernel exchange" if ffn.use_fused else "NCCL all-reduce",
+                                                 "parity": par}
+            ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+            ffn.destroy()
+            del ffn
+            torch.cuda.empty_cache()
         stack = None
     if dist is not None:
         dist.barrier()
@@ -366,12 +428,31 @@ def main():
         "clocks": clocks,
     }
     if tp_extra is not None:
-        out["extra"] = {"q4_70b_ffn_m1_tp": tp_extra}
+        out["extra"] = tp_extra
     if world == 1 and not args.no_extra:
+        # the same graph replayed for at least two seconds, with the SM clock sampled beside it
+        reps = max(200, int(2.2e3 / ms_per_step))
+        sampler2 = ClockSampler(local_rank)
+        sampler2.start()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stack.stream):
+            s0.record()
+            for _ in range(reps):
+                stack.step()
+            s1.record()
+        torch.cuda.synchronize()
+        sus_ms = s0.elapsed_time(s1) / reps
+        clk2 = sampler2.stop()
+        sustained = {"steps": reps, "seconds": sus_ms * reps / 1e3, "tokens_per_s": 1e3 / sus_ms, "frac_of_hbm_peak": stack.bytes_per_step / (sus_ms * 1e-3) / 1e9 / peak,
+                     "sm_mhz_median": clk2["sm_mhz"], "reasons": clk2["reasons"], "samples": clk2["samples"],
+                     "tokens_per_s_per_ghz": (1e3 / sus_ms) / (clk2["sm_mhz"] / 1e3) if clk2["sm_mhz"] else None}
         stack.destroy()
         del stack
         torch.cuda.empty_cache()
         out["extra"] = extras(ctx, peak)
+        out["extra"]["sustained"] = sustained
+        out["roofline"]["frac_of_read_only_peak"] = achieved / out["extra"]["hbm_read_only_gbs"]
+        out["roofline"]["frac_of_nominal_8tbs"] = achieved / 8000.0
         ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
     if world == 1:
         toks_cpu, dt = cpu_arm(args.cpu_steps, 2, threads)

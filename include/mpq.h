@@ -43,6 +43,8 @@ extern "C" {
 #define MPQ_ERR_UNSUPPORTED    -5   /* device is not sm_100, or size beyond a stated maximum */
 #define MPQ_ERR_PEER_TIMEOUT   -6   /* a bounded device-side wait on a peer flag ran out */
 #define MPQ_ERR_STATE          -7   /* call order violated (e.g. exchange used before peers were attached) */
+#define MPQ_ERR_FORMAT         -8   /* file is not a weight container this build can use (magic, version, layout, checksum) */
+#define MPQ_ERR_IO             -9   /* file cannot be opened, read or written */
 
 #define MPQ_FMT_Q4     1
 #define MPQ_FMT_NVFP4  2
@@ -73,9 +75,11 @@ int32_t mpq_context_info(const mpq_context* ctx, mpq_device_info* out);
 const char* mpq_status_string(int32_t status);
 /* Text of the last error recorded on this context (thread-compatible, not thread-safe). */
 const char* mpq_last_error(const mpq_context* ctx);
-/* Reads the device-side status word (this synchronises with all prior work on
- * the GPU).  MPQ_ERR_PEER_TIMEOUT if a bounded wait inside a kernel ran out
- * since the last poll; the word is then cleared. */
+/* Reads the device-side status words (this synchronises with all prior work on
+ * the GPU): the Q4 and NVFP4 kernels' and, once mpq_q4_linear_forward_static
+ * has run on this device, the one inside its static array.
+ * MPQ_ERR_PEER_TIMEOUT if a bounded wait inside a kernel ran out since the
+ * last poll; the word is then cleared. */
 int32_t mpq_context_poll_status(mpq_context* ctx);
 /* Number of kernels this context has launched since creation. */
 int64_t mpq_context_launch_count(const mpq_context* ctx);
@@ -103,7 +107,9 @@ int32_t mpq_nvfp4_weight_create(mpq_context* ctx, int64_t N, int64_t K,
 /* ---- any weight ---------------------------------------------------------- */
 int32_t mpq_weight_shape(const mpq_weight* w, int64_t* N, int64_t* K, int32_t* fmt);
 /* Exact fp32 export [N][K] read back FROM THE DEVICE LAYOUT (the bit-exact
- * criterion: proves the repack preserved every value). */
+ * criterion: proves the repack preserved every value): the Q4 tile stream,
+ * or the NVFP4 codes with the scale factors un-tiled from the order the GEMM
+ * consumes (the device keeps no other copy of them). */
 int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, float* out_dev, void* stream);
 int64_t mpq_weight_device_bytes(const mpq_weight* w);
 int32_t mpq_weight_destroy(mpq_weight* w);
@@ -112,10 +118,11 @@ int32_t mpq_weight_destroy(mpq_weight* w);
 /* Forward calls on one context share that context's scratch buffers: issue
  * them in stream order (one stream per context at a time).
  * Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
- * row-major device arrays, 16-byte aligned.  Any M >= 1 (M <= 16 is one
- * launch; larger M runs in slabs of 16 rows).  Finite inputs with |x| < 3e38
- * are handled at any magnitude (each CTA renormalises its slice by a power
- * of two); a non-finite x yields non-finite outputs in its row. */
+ * row-major device arrays, 16-byte aligned.  Any M >= 1 (M <= 4 is one
+ * launch of the streaming kernel; larger M runs as several launches over
+ * slabs of rows).  Finite inputs with |x| < 3e38 are handled at any magnitude
+ * (each CTA renormalises its slice by a power of two); a non-finite x yields
+ * non-finite outputs in its row. */
 int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
                               float* y_dev, void* stream);
 /* Same result as mpq_q4_linear_forward for callers that must not let the
@@ -129,8 +136,11 @@ int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float
  * MPQ_ERR_UNSUPPORTED.  All calls on one device share that array: they must be
  * ordered on the GPU (calls that overlap there race on the slots).  The slots
  * are empty again after every completed call, so nothing needs clearing
- * between calls.  If a bounded wait ran out (status_dev non-zero), slots may be
- * left full: do not use this entry point again on that device in this process.
+ * between calls.  If a bounded wait ran out, slots may be left full: with a
+ * status_dev the caller sees it there and must not use this entry point again
+ * on that device in this process; without one the kernel records it in a word
+ * of the static array that mpq_context_poll_status reads (and, on a timeout,
+ * clears together with the slots -- that poll may copy, but allocates nothing).
  * The first call on a device looks up the array's device
  * address and raises the kernels' shared-memory limit; make that call before
  * any stream capture.  status_dev, if not NULL, is a caller-owned device int
@@ -163,6 +173,11 @@ int32_t mpq_exchange_buffer(mpq_exchange* ex, void** dev_ptr, int64_t* bytes);
 /* Polls a rank waits for one element of a peer's partial output before it gives up,
  * records MPQ_ERR_PEER_TIMEOUT in the context's status word and returns (default 2^22). */
 int32_t mpq_exchange_set_wait_limit(mpq_exchange* ex, uint32_t polls);
+/* Call after ending a stream capture that recorded calls on this exchange: MPQ_ERR_STATE
+ * if the captured graph holds an odd number of them (such a graph must not be replayed,
+ * see below), MPQ_OK otherwise.  Clears the condition.  Without this call the next
+ * forward call on the exchange reports the same condition. */
+int32_t mpq_exchange_graph_check(mpq_exchange* ex);
 int32_t mpq_exchange_destroy(mpq_exchange* ex);
 /* Row-parallel linear with the sum over ranks fused into the kernel:
  * Y[M][N] = sum_r X_r[M][K/world] . W_r^T on every rank.  Every rank must make the
@@ -185,9 +200,53 @@ int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, m
 int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
                                const uint8_t* a_codes_dev, const uint8_t* a_sf_dev, float a_tensor_scale,
                                int64_t M, uint16_t* c_bf16_dev, void* stream);
+/* Quantises activations to canonical NVFP4 on the GPU, ready to be the GEMM's A: X[M][K] fp32 (or
+ * bf16 bits when x_is_bf16 != 0) -> codes [M][K/2], sf [M][K/16].  Per 16-element block the scale
+ * byte is e4m3(amax / (6 * tensor_scale)) and each element e2m1(x / (scale * tensor_scale)), both
+ * round-to-nearest-even and saturating; a block whose scale encodes to 0 gets zero codes.  K must
+ * be a multiple of 16; non-finite inputs are not supported. */
+int32_t mpq_nvfp4_quantize_activations(mpq_context* ctx, const void* x_dev, int32_t x_is_bf16, int64_t M, int64_t K,
+                                       float tensor_scale, uint8_t* codes_dev, uint8_t* sf_dev, void* stream);
 /* Exact fp32 export [R][K] of a canonical NVFP4 tensor on the device. */
 int32_t mpq_nvfp4_dequantize(mpq_context* ctx, int64_t R, int64_t K, const uint8_t* codes_dev,
                              const uint8_t* sf_dev, float tensor_scale, float* out_dev, void* stream);
+
+/* ---- weight container ------------------------------------------------------- */
+/* Files of two kinds, one 128-byte versioned header + payload + FNV-1a checksum each:
+ *   MPQ_FILE_CANONICAL  the interchange arrays (Q4: codes + fp16 scale bits; NVFP4: codes + e4m3 scales +
+ *                       tensor scale), readable by any build;
+ *   MPQ_FILE_DEVICE     a weight exactly as it lies in device memory (Q4 tile stream; NVFP4 codes + tiled
+ *                       scale factors), so that loading needs no repack pass.  It is a CACHE: a file whose
+ *                       layout version or geometry is not this build's is refused with MPQ_ERR_FORMAT and
+ *                       the caller rebuilds the weight from its canonical arrays (the reference keeps its
+ *                       compiled shader binaries the same way, platform/src/os/linux/opengl.rs:611-640).
+ * mpq_canonical_* need no GPU.  scales_host is uint16[N][K/32] for Q4, uint8[N][K/16] for NVFP4. */
+#define MPQ_FILE_CANONICAL 1
+#define MPQ_FILE_DEVICE    2
+typedef struct mpq_file_info_t {
+    int32_t kind, fmt, layout_version, reserved;
+    int64_t N, K;
+    int64_t bytes_a, bytes_b;      /* canonical: codes, scales; device: the layout's two buffers */
+    float tensor_scale;
+    int32_t reserved2;
+} mpq_file_info_t;
+int32_t mpq_file_info(const char* path, mpq_file_info_t* out);
+int32_t mpq_canonical_save(const char* path, int32_t fmt, int64_t N, int64_t K, const uint8_t* codes_host,
+                           const void* scales_host, float tensor_scale);
+int32_t mpq_canonical_load(const char* path, uint8_t* codes_host, int64_t codes_capacity, void* scales_host,
+                           int64_t scales_capacity, float* tensor_scale);
+int32_t mpq_weight_save(mpq_context* ctx, const mpq_weight* w, const char* path);
+int32_t mpq_weight_load(mpq_context* ctx, const char* path, mpq_weight** out);
+
+/* ---- measured ceilings ------------------------------------------------------ */
+/* Two probes for whoever reports roofline fractions of the kernels above (no counterpart in the
+ * reference; the caller times them with events on `stream`).
+ * mpq_probe_hbm_read streams `bytes` of device memory once, read-only, with the loads the Q4 kernels
+ * use (out_dev: a device word that is practically never written).  Use a buffer larger than L2.
+ * mpq_probe_fp4_mma has every SM issue mmas_per_sm block-scaled FP4 MMAs of the GEMM's own shape
+ * (128 x 224 x 64) back to back from resident operands; *flop_out = the flop the launch executes. */
+int32_t mpq_probe_hbm_read(mpq_context* ctx, const void* buf_dev, int64_t bytes, uint32_t* out_dev, void* stream);
+int32_t mpq_probe_fp4_mma(mpq_context* ctx, int32_t mmas_per_sm, double* flop_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,7 @@
 #include <string>
 
 #include "nvfp4.cuh"
+#include "per_device.h"
 #include "q4.cuh"
 
 using namespace mpq;
@@ -34,13 +35,15 @@ struct mpq_context {
     // scratch of the streaming Q4 kernel: tagged partial tiles of row pair-tiles cut by a boundary
     // between two CTAs' runs (two slots per CTA; write-once / read-once per launch), one status word
     uint2* q4_partials;
-    int q4_partials_warps;
+    int q4_partials_ctas;
     int* q4_status;
     bool q4_stream;           // use the streaming kernel where the activation fits in shared memory
-    int q4_group;             // chunks per bulk copy of the streaming kernel (2 or 4)
     bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
+    bool q4_coresident;       // size a launch for half an SM where the activation allows it
+    int q4_group;             // chunks per bulk copy of the streaming kernel: 0 = choose, 1 or 2
     int q4_depth;             // most ring stages per warp
-    int q4_pre;               // stages copied before the dependency resolves
+    int q4_depth_full;        // ... of a CTA that has an SM to itself
+    int q4_pre;               // stages copied before the dependency resolves (-1 = choose)
     bool q4_slab4;            // M > 4 as slabs of four rows through the streaming kernel
     Nvfp4Scratch fp4;
 };
@@ -63,10 +66,15 @@ struct mpq_exchange {
     bool attached;
     uint32_t calls;              // launches so far: its parity picks the half of the buffer
     uint32_t wait_limit;
+    // calls recorded into the stream capture in progress (a replayed graph must hold an even number)
+    bool cap_active, cap_odd;
+    unsigned long long cap_id;
+    uint32_t cap_calls;
 };
 
 static const uint32_t CTX_MAGIC = 0x4D505143u, W_MAGIC = 0x4D505157u, X_MAGIC = 0x4D505158u;
 static bool x_ok(const mpq_exchange* x) { return x && x->magic == X_MAGIC; }
+static int32_t exchange_note_call(mpq_context* ctx, mpq_exchange* ex, cudaStream_t s);
 
 static int32_t fail(mpq_context* ctx, int32_t code, const char* fmt, ...)
 {
@@ -103,6 +111,8 @@ extern "C" const char* mpq_status_string(int32_t s)
         case MPQ_ERR_UNSUPPORTED: return "unsupported device or size";
         case MPQ_ERR_PEER_TIMEOUT: return "peer wait timed out";
         case MPQ_ERR_STATE: return "invalid call order";
+        case MPQ_ERR_FORMAT: return "not a usable weight container";
+        case MPQ_ERR_IO: return "file cannot be opened, read or written";
         default: return "unknown status";
     }
 }
@@ -121,7 +131,7 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->hx = c->hy = nullptr;
     c->hx_bytes = c->hy_bytes = 0;
     c->q4_partials = nullptr;
-    c->q4_partials_warps = 0;
+    c->q4_partials_ctas = 0;
     c->q4_status = nullptr;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&c->prop, device) != cudaSuccess) {
         delete c;
@@ -137,12 +147,16 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_variant = (e && e[0] == '1') ? 1 : 0;
     e = getenv("MPQ_Q4_STREAM");
     c->q4_stream = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_CORESIDENT");
+    c->q4_coresident = e && e[0] == '1';          // measured slower than one CTA per SM so far: opt-in
     e = getenv("MPQ_Q4_GROUP");
-    c->q4_group = (e && e[0] == '4') ? 4 : 2;
+    c->q4_group = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_DEPTH");
-    c->q4_depth = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    c->q4_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 8;
+    e = getenv("MPQ_Q4_DEPTH_FULL");
+    c->q4_depth_full = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_PRE");
-    c->q4_pre = (e && e[0] >= '0' && e[0] <= '4') ? e[0] - '0' : 1;
+    c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : -1;
     e = getenv("MPQ_Q4_SLAB4");
     c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
@@ -328,8 +342,7 @@ extern "C" int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, 
         q4_dequant_kernel<<<(unsigned)((words + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint32_t*>(q.stream), q.N, q.K,
                                                                            q.nrp, q.nchunks, out_dev);
     } else {
-        const Nvfp4Dev& f = w->fp4;
-        nvfp4_dequant_launch(f.codes, f.sf_canonical, f.tensor_scale, f.N, f.K, out_dev, s);
+        nvfp4_weight_dequant_launch(w->fp4, out_dev, s);
     }
     ctx->launches += 1;
     CU_TRY(ctx, cudaGetLastError());
@@ -340,14 +353,14 @@ extern "C" int32_t mpq_weight_dequantize(mpq_context* ctx, const mpq_weight* w, 
 // Q4 linear
 // ---------------------------------------------------------------------------
 template <int MT, bool SUBN>
-static cudaError_t q4_launch_t(const Q4Launch& p, dim3 grid, size_t smem, bool pdl, cudaStream_t s)
+static cudaError_t q4_launch_t(int device, const Q4Launch& p, dim3 grid, size_t smem, bool pdl, cudaStream_t s)
 {
     auto kern = q4_linear_kernel<MT, SUBN>;
-    static bool configured = false;        // per instantiation; static + dynamic shared memory may pass 48 KiB
-    if (!configured) {
+    static PerDeviceOnce configured;       // per instantiation and device; static + dynamic shared memory may pass 48 KiB
+    if (configured.needs(device)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(160 * 1024));
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -373,65 +386,81 @@ static cudaError_t q4_launch_t(const Q4Launch& p, dim3 grid, size_t smem, bool p
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-// Scratch of the streaming kernel, allocated on first use and kept for the context's life.
-static const int Q4S_MAX_WARPS = 32 * 1024;    // up to four CTAs of 8 warps on up to 1024 SMs
-static int32_t q4_stream_scratch(mpq_context* ctx, int warps)
+// Scratch of the streaming kernel, allocated on first use and kept for the context's life: two tagged
+// partial-tile slots (2 KiB) per CTA of the largest grid seen so far.
+static int32_t q4_stream_scratch(mpq_context* ctx, int ctas)
 {
     if (!ctx->q4_status) {
         CU_TRY(ctx, cudaMalloc(&ctx->q4_status, sizeof(int)));
         CU_TRY(ctx, cudaMemset(ctx->q4_status, 0, sizeof(int)));
     }
-    if (ctx->q4_partials_warps < warps) {
+    if (ctx->q4_partials_ctas < ctas) {
         CU_TRY(ctx, cudaDeviceSynchronize());          // nobody may still be using the old array
         cudaFree(ctx->q4_partials);
         ctx->q4_partials = nullptr;
-        ctx->q4_partials_warps = 0;
-        int n = std::max(warps, 4096);
-        size_t bytes = (size_t)n * 2 * 32 * 4 * sizeof(uint2);
+        ctx->q4_partials_ctas = 0;
+        int n = std::max(ctas, 1024);
+        size_t bytes = (size_t)n * Q4S_SLOT_BYTES_PER_CTA;
         CU_TRY(ctx, cudaMalloc(&ctx->q4_partials, bytes));
         CU_TRY(ctx, cudaMemset(ctx->q4_partials, 0, bytes));      // tag 0 = empty slot
-        ctx->q4_partials_warps = n;
+        ctx->q4_partials_ctas = n;
     }
     return MPQ_OK;
 }
 
 // The streaming kernel applies when M <= 4 and the staged activation plus a ring fit in shared memory.
-struct Q4StreamPlan { int depth, G, nx, ctas_per_sm; size_t smem; };
+// Preferred form: a launch takes less than half of an SM (shared memory, and 64 registers per thread), so
+// that the next launch's CTA is resident -- and prefetching -- beside this one; else one CTA per SM.
+struct Q4StreamPlan { int depth, G, nw, minb, pre; size_t smem; };
+static const size_t Q4S_STATIC_SMEM = 512;                 // s_max, wrp, zero page, rounded up
 static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4StreamPlan* pl)
 {
     if (!ctx->q4_stream || M > 4) return false;
-    size_t nblk = (size_t)q.nchunks * 2;
-    size_t xbytes = nblk * (2 * M) * 64 + nblk * M * 16 + 8 * 8 * Q4S_WARPS;
-    int need = (M * q.nchunks + 31) / 32;                 // float4 of x per thread (512 threads)
-    pl->nx = need <= 4 ? 4 : need <= 8 ? 8 : need <= 16 ? 16 : 0;
-    pl->ctas_per_sm = 1;
-    // one CTA per SM: 227 KiB less the kernel's static shared memory (17 KiB) and the 1 KiB the system reserves
-    const size_t budget = (size_t)(227 - 18) * 1024;
-    const int prefer = ctx->q4_group;
-    for (int pass = 0; pass < 2; ++pass) {
-        const int G = pass == 0 ? prefer : (prefer == 4 ? 2 : 4);
-        const size_t stage = (size_t)Q4S_WARPS * G * Q4_UNIT_BYTES;
-        for (int d = std::min(ctx->q4_depth, G == 4 ? 2 : 4); d >= 1; --d) {
-            size_t total = stage * d + xbytes;
-            if (total <= budget) { pl->G = G; pl->depth = d; pl->smem = total; return true; }
+    // the ring with the most bytes that fits (ties: the larger copies), at least dmin stages deep
+    auto fit = [&](int nw, size_t budget, int dmax, int dmin) {
+        const size_t fixed = (size_t)q.nchunks * 256 * M + (size_t)q.nchunks * 16 * M + (size_t)nw * Q4S_MAX_DEPTH * 8;
+        size_t best = 0;
+        pl->nw = nw;
+        for (int G = 2; G >= 1; --G) {
+            if (ctx->q4_group && G != ctx->q4_group) continue;
+            const size_t stage = (size_t)nw * G * Q4_UNIT_BYTES;
+            if (fixed + stage * dmin > budget) continue;
+            const int d = (int)std::min<size_t>((size_t)dmax, (budget - fixed) / stage);
+            if (stage * d > best) { best = stage * d; pl->G = G; pl->depth = d; pl->smem = fixed + stage * d; }
         }
+        return best != 0;
+    };
+    // an SM has 228 KiB of shared memory, a CTA may use 227 KiB, and the system reserves 1 KiB per resident CTA
+    const size_t half = (size_t)114 * 1024 - 1024 - Q4S_STATIC_SMEM;
+    const size_t full = (size_t)227 * 1024 - Q4S_STATIC_SMEM;
+    const int dmax = std::min(ctx->q4_depth, Q4S_MAX_DEPTH);
+    if (ctx->q4_coresident && fit(Q4S_WARPS_HALF, half, dmax, 2)) {
+        pl->minb = 2;
+        pl->pre = ctx->q4_pre < 0 ? pl->depth : ctx->q4_pre;
+        return true;
+    }
+    if (fit(Q4S_WARPS_FULL, full, std::min(dmax, ctx->q4_depth_full), 1)) {
+        pl->minb = 1;
+        pl->pre = ctx->q4_pre < 0 ? 1 : ctx->q4_pre;
+        return true;
     }
     return false;
 }
 
-template <bool SUBN, int G, int NX, int MINB>
-static cudaError_t q4_stream_launch_t(const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
+template <int G, int NW, int MINB>
+static cudaError_t q4_stream_launch_t(int device, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
 {
-    auto kern = q4_stream_kernel<SUBN, G, NX, MINB>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(209 * 1024));
+    auto kern = q4_stream_kernel<G, NW, MINB>;
+    static PerDeviceOnce configured;                      // the attribute is per device, not per process
+    if (configured.needs(device)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - Q4S_STATIC_SMEM));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
-        configured = true;
+        configured.mark(device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(Q4S_THREADS);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -442,51 +471,69 @@ static cudaError_t q4_stream_launch_t(const Q4StreamLaunch& p, int grid, size_t 
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
-template <bool SUBN, int G>
-static cudaError_t q4_stream_launch_nx(int nx, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
+// Launch parameters of the streaming kernel for one slab of M <= 4 rows, everything but the scratch
+// pointers and the exchange; returns the grid size.  Shared by every entry point that launches it.
+static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4StreamPlan& pl, const float* x, int M, float* y,
+                            int64_t ldy, Q4StreamLaunch* p)
 {
-    switch (nx) {
-        case 4: return q4_stream_launch_t<SUBN, G, 4, 1>(p, grid, smem, pdl, s);
-        case 8: return q4_stream_launch_t<SUBN, G, 8, 1>(p, grid, smem, pdl, s);
-        case 16: return q4_stream_launch_t<SUBN, G, 16, 1>(p, grid, smem, pdl, s);
-        default: return q4_stream_launch_t<SUBN, G, 0, 1>(p, grid, smem, pdl, s);
-    }
+    const int sms = ctx->prop.multiProcessorCount;
+    const int groups = (int)(q.units() / pl.G);
+    const int W = (int)std::min<int64_t>((int64_t)sms * pl.nw, groups);
+    // whole row pair-tiles per CTA when there is about one per SM or more: no tile is then shared between CTAs
+    p->tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
+    p->nrp = q.nrp;
+    p->stream = q.stream; p->X = x; p->Y = y; p->M = M; p->N = (int)q.N; p->K = (int)q.K; p->ldy = ldy;
+    p->nchunks = q.nchunks; p->groups = groups; p->warps_total = W; p->depth = pl.depth; p->pre = pl.pre;
+    p->partials = nullptr; p->status = nullptr;
+    p->xworld = 0; p->xrank = 0; p->xslot = 0; p->xlimit = 0;
+    for (int r = 0; r < 8; ++r) p->xpeer[r] = nullptr;
+    return p->tile_mode ? std::min(sms, q.nrp) : (W + pl.nw - 1) / pl.nw;
+}
+
+#ifdef MPQ_TRACE
+// Diagnostic build: launch i of the process stamps its CTAs' phase times into slot i % 64 of a managed array.
+static unsigned long long* g_trace = nullptr;
+static int g_trace_n = 0;
+extern "C" unsigned long long* mpq_debug_trace(int32_t* launches)
+{
+    if (launches) *launches = g_trace_n;
+    return g_trace;
+}
+#endif
+
+static int32_t q4_stream_enqueue(mpq_context* ctx, const Q4StreamPlan& pl, const Q4StreamLaunch& p_in, int grid, cudaStream_t s)
+{
+#ifdef MPQ_TRACE
+    Q4StreamLaunch p = p_in;
+    if (!g_trace && cudaMallocManaged(&g_trace, (size_t)64 * 1024 * 8 * 8) != cudaSuccess) g_trace = nullptr;
+    p.trace = (g_trace && grid <= 1024) ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 8 : nullptr;
+#else
+    const Q4StreamLaunch& p = p_in;
+#endif
+    cudaError_t e;
+    if (pl.minb == 2) e = pl.G == 2 ? q4_stream_launch_t<2, Q4S_WARPS_HALF, 2>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1, Q4S_WARPS_HALF, 2>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
+    else e = pl.G == 2 ? q4_stream_launch_t<2, Q4S_WARPS_FULL, 1>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1, Q4S_WARPS_FULL, 1>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
+    ctx->launches += 1;
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
+    return MPQ_OK;
 }
 
 // The streaming kernel for one slab of M <= 4 rows; with an exchange it also adds the ranks' partial outputs.
 static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4StreamPlan& pl, const float* x, int M, float* y,
                                  int64_t ldy, mpq_exchange* ex, cudaStream_t s)
 {
-    {
-        const int sms = ctx->prop.multiProcessorCount;
-        const int groups = (int)(q.units() / pl.G);
-        int W = (int)std::min<int64_t>((int64_t)sms * Q4S_WARPS, groups);
-        W = std::min(W, Q4S_MAX_WARPS);
-        int32_t st = q4_stream_scratch(ctx, W);
-        if (st) return st;
-        Q4StreamLaunch p;
-        // whole row pair-tiles per CTA when there is about one per SM or more: no tile is then shared between CTAs
-        p.tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
-        p.nrp = q.nrp;
-        p.stream = q.stream; p.X = x; p.Y = y; p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
-        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth; p.pre = ctx->q4_pre;
-        p.partials = ctx->q4_partials; p.status = ctx->q4_status;
-        p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
-        for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
-        if (ex) {
-            const size_t half = (size_t)(++ex->calls & 1u) * ex->world * ex->max_floats;
-            p.xworld = ex->world; p.xrank = ex->rank; p.xslot = ex->max_floats; p.xlimit = ex->wait_limit;
-            for (int r = 0; r < ex->world; ++r) p.xpeer[r] = ex->peer[r] + half;
-        }
-        int grid = p.tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
-        cudaError_t e;
-        const bool subn = ctx->q4_variant == 0;
-        if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
-        else e = subn ? q4_stream_launch_nx<true, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
-        ctx->launches += 1;
-        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
-        return MPQ_OK;
+    Q4StreamLaunch p;
+    const int grid = q4_stream_params(ctx, q, pl, x, M, y, ldy, &p);
+    int32_t st = q4_stream_scratch(ctx, grid);
+    if (st) return st;
+    p.partials = ctx->q4_partials; p.status = ctx->q4_status;
+    if (ex) {
+        if ((st = exchange_note_call(ctx, ex, s))) return st;
+        const size_t half = (size_t)(++ex->calls & 1u) * ex->world * ex->max_floats;
+        p.xworld = ex->world; p.xrank = ex->rank; p.xslot = ex->max_floats; p.xlimit = ex->wait_limit;
+        for (int r = 0; r < ex->world; ++r) p.xpeer[r] = ex->peer[r] + half;
     }
+    return q4_stream_enqueue(ctx, pl, p, grid, s);
 }
 
 // One launch for a slab of M <= 16 activation rows.
@@ -519,9 +566,10 @@ static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float*
     dim3 grid((unsigned)q.nrp, (unsigned)splits);
     cudaError_t e;
     const bool subn = ctx->q4_variant == 0;
-    if (MT == 1) e = subn ? q4_launch_t<1, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<1, false>(p, grid, smem, ctx->pdl, s);
-    else if (MT == 2) e = subn ? q4_launch_t<2, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<2, false>(p, grid, smem, ctx->pdl, s);
-    else e = subn ? q4_launch_t<4, true>(p, grid, smem, ctx->pdl, s) : q4_launch_t<4, false>(p, grid, smem, ctx->pdl, s);
+    const int dev = ctx->device;
+    if (MT == 1) e = subn ? q4_launch_t<1, true>(dev, p, grid, smem, ctx->pdl, s) : q4_launch_t<1, false>(dev, p, grid, smem, ctx->pdl, s);
+    else if (MT == 2) e = subn ? q4_launch_t<2, true>(dev, p, grid, smem, ctx->pdl, s) : q4_launch_t<2, false>(dev, p, grid, smem, ctx->pdl, s);
+    else e = subn ? q4_launch_t<4, true>(dev, p, grid, smem, ctx->pdl, s) : q4_launch_t<4, false>(dev, p, grid, smem, ctx->pdl, s);
     ctx->launches += 1;
     if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_linear_kernel launch failed: %s", cudaGetErrorString(e));
     return MPQ_OK;
@@ -612,11 +660,12 @@ extern "C" int32_t mpq_q4_linear_forward_host(mpq_context* ctx, const mpq_weight
 // allocates lazily (the streaming kernel's scratch, on a context's first call); this variant never
 // does.  Its scratch is the array below, which every GPU that loads the library holds until exit.
 constexpr int Q4_STATIC_MAX_CTAS = 512;                                   // two CTAs per SM on up to 256 SMs
-constexpr size_t Q4_STATIC_SLOT_BYTES = (size_t)Q4_STATIC_MAX_CTAS * 2 * 32 * 4 * sizeof(uint2);   // 1 MiB
+constexpr size_t Q4_STATIC_SLOT_BYTES = (size_t)Q4_STATIC_MAX_CTAS * Q4S_SLOT_BYTES_PER_CTA;   // 1 MiB
+// first 256 bytes: the status word used when the caller passes none; then the slots
 static __device__ __align__(256) unsigned char g_q4_static_scratch[256 + Q4_STATIC_SLOT_BYTES];
 // In host code the array's name is only a stand-in: the device address comes from cudaGetSymbolAddress,
 // once per device, with that device current.
-static unsigned char* g_q4_static_ptr[64] = {};
+static unsigned char* g_q4_static_ptr[PerDeviceOnce::MAX_DEVICES] = {};
 
 extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
                                                 float* y_dev, int32_t* status_dev, void* stream)
@@ -624,7 +673,7 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
     int32_t st = q4_validate(ctx, w, x_dev, M, y_dev);
     if (st) return st;
     if (!aligned16(x_dev) || !aligned16(y_dev)) return fail(ctx, MPQ_ERR_ALIGN, "x and y must be 16-byte aligned");
-    if (ctx->device < 0 || ctx->device >= 64) return fail(ctx, MPQ_ERR_UNSUPPORTED, "device index %d beyond the static table", ctx->device);
+    if (ctx->device < 0 || ctx->device >= PerDeviceOnce::MAX_DEVICES) return fail(ctx, MPQ_ERR_UNSUPPORTED, "device index %d beyond the static table", ctx->device);
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     if (!g_q4_static_ptr[ctx->device]) {                  // set-up: the first call on this device
         void* p = nullptr;
@@ -645,27 +694,13 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
             if (st) return st;
             continue;
         }
-        const int sms = ctx->prop.multiProcessorCount;
-        const int groups = (int)(q.units() / pl.G);
-        const int W = (int)std::min<int64_t>((int64_t)sms * Q4S_WARPS, groups);
-        const int tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
-        const int grid = tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
+        Q4StreamLaunch p;
+        const int grid = q4_stream_params(ctx, q, pl, x, m, y, q.N, &p);
         if (grid > Q4_STATIC_MAX_CTAS)
             return fail(ctx, MPQ_ERR_UNSUPPORTED, "this launch needs %d scratch slots, the static array holds %d", grid, Q4_STATIC_MAX_CTAS);
-        Q4StreamLaunch p;
-        p.stream = q.stream; p.X = x; p.Y = y; p.M = m; p.N = (int)q.N; p.K = (int)q.K; p.ldy = q.N;
-        p.nchunks = q.nchunks; p.groups = groups; p.warps_total = W; p.depth = pl.depth; p.pre = ctx->q4_pre;
-        p.tile_mode = tile_mode; p.nrp = q.nrp;
         p.partials = reinterpret_cast<uint2*>(base + 256);
         p.status = status_dev ? status_dev : reinterpret_cast<int*>(base);
-        p.xworld = 0; p.xrank = 0; p.xslot = 0; p.xlimit = 0;
-        for (int r = 0; r < 8; ++r) p.xpeer[r] = nullptr;
-        cudaError_t e;
-        const bool subn = ctx->q4_variant == 0;
-        if (pl.G == 4) e = subn ? q4_stream_launch_nx<true, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 4>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
-        else e = subn ? q4_stream_launch_nx<true, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_nx<false, 2>(pl.nx, p, grid, pl.smem, ctx->pdl, s);
-        ctx->launches += 1;
-        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
+        if ((st = q4_stream_enqueue(ctx, pl, p, grid, s))) return st;
     }
     return MPQ_OK;
 }
@@ -685,6 +720,7 @@ extern "C" int32_t mpq_exchange_create(mpq_context* ctx, int32_t rank, int32_t w
     if (!x) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
     x->magic = X_MAGIC; x->device = ctx->device; x->rank = rank; x->world = world; x->max_floats = max_floats;
     x->calls = 0; x->wait_limit = 1u << 22; x->attached = world == 1;
+    x->cap_active = x->cap_odd = false; x->cap_id = 0; x->cap_calls = 0;
     for (int r = 0; r < 8; ++r) { x->peer[r] = nullptr; x->opened[r] = false; }
     size_t bytes = (size_t)2 * world * max_floats * sizeof(uint2);
     cudaError_t e = cudaMalloc(&x->local, bytes);
@@ -755,6 +791,45 @@ extern "C" int32_t mpq_exchange_set_wait_limit(mpq_exchange* x, uint32_t polls)
     return MPQ_OK;
 }
 
+// Consecutive calls alternate between the halves of the buffer, so a graph that is replayed must hold an even
+// number of calls on one exchange: with an odd number, two consecutive replays would start on the same half
+// and a fast rank could overwrite what a slow one has not read.  The count is kept per stream capture; a
+// capture that ended on an odd count is reported by mpq_exchange_graph_check and by the next forward call.
+static void exchange_close_capture(mpq_exchange* ex)
+{
+    if (ex->cap_active && (ex->cap_calls & 1u)) ex->cap_odd = true;
+    ex->cap_active = false;
+}
+
+static int32_t exchange_note_call(mpq_context* ctx, mpq_exchange* ex, cudaStream_t s)
+{
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    unsigned long long id = 0;
+    if (cudaStreamGetCaptureInfo(s, &cs, &id) != cudaSuccess) {
+        cudaGetLastError();
+        cs = cudaStreamCaptureStatusNone;
+    }
+    const bool capturing = cs == cudaStreamCaptureStatusActive;
+    if (ex->cap_active && (!capturing || id != ex->cap_id)) exchange_close_capture(ex);
+    if (ex->cap_odd)
+        return fail(ctx, MPQ_ERR_STATE, "a captured graph holds an odd number of calls on this exchange (%u): capture an even number, "
+                                        "then clear the condition with mpq_exchange_graph_check", ex->cap_calls);
+    if (capturing) {
+        if (!ex->cap_active) { ex->cap_active = true; ex->cap_id = id; ex->cap_calls = 0; }
+        ++ex->cap_calls;
+    }
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_exchange_graph_check(mpq_exchange* x)
+{
+    if (!x_ok(x)) return MPQ_ERR_INVALID_ARG;
+    exchange_close_capture(x);
+    const bool odd = x->cap_odd;
+    x->cap_odd = false;
+    return odd ? MPQ_ERR_STATE : MPQ_OK;
+}
+
 extern "C" int32_t mpq_exchange_destroy(mpq_exchange* x)
 {
     if (!x_ok(x)) return MPQ_ERR_INVALID_ARG;
@@ -788,16 +863,20 @@ extern "C" int32_t mpq_context_poll_status(mpq_context* ctx)
 {
     if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
     CU_TRY(ctx, cudaSetDevice(ctx->device));
-    int* words[2] = {ctx->q4_status, ctx->fp4.status};
-    for (int i = 0; i < 2; ++i) {
+    // the third word is the one mpq_q4_linear_forward_static uses when its caller passes no status pointer
+    unsigned char* stat = (ctx->device >= 0 && ctx->device < PerDeviceOnce::MAX_DEVICES) ? g_q4_static_ptr[ctx->device] : nullptr;
+    int* words[3] = {ctx->q4_status, ctx->fp4.status, reinterpret_cast<int*>(stat)};
+    const char* names[3] = {"Q4", "NVFP4 GEMM", "Q4 static-scratch"};
+    for (int i = 0; i < 3; ++i) {
         if (!words[i]) continue;
         int v = 0;
         CU_TRY(ctx, cudaMemcpy(&v, words[i], sizeof(int), cudaMemcpyDeviceToHost));    // synchronises with prior work
         if (v == 0) continue;
         cudaMemset(words[i], 0, sizeof(int));            // a wait ran out: clear the word for the next launch
         if (i == 0 && ctx->q4_partials)                  // ... and the slots the aborted launch may have left full
-            cudaMemset(ctx->q4_partials, 0, (size_t)ctx->q4_partials_warps * 2 * 32 * 4 * sizeof(uint2));
-        return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (%s kernel, code %d)", i ? "NVFP4 GEMM" : "Q4", v);
+            cudaMemset(ctx->q4_partials, 0, (size_t)ctx->q4_partials_ctas * Q4S_SLOT_BYTES_PER_CTA);
+        if (i == 2) cudaMemset(stat + 256, 0, Q4_STATIC_SLOT_BYTES);
+        return fail(ctx, MPQ_ERR_PEER_TIMEOUT, "a bounded device-side wait ran out (%s kernel, code %d)", names[i], v);
     }
     return MPQ_OK;
 }
@@ -846,7 +925,7 @@ extern "C" int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
     CU_TRY(ctx, cudaSetDevice(ctx->device));
     std::string err;
     int launches = 0;
-    int32_t st = nvfp4_gemm_launch(ctx->fp4, w->fp4, a_codes_dev, a_sf_dev, a_tensor_scale, M, c_bf16_dev,
+    int32_t st = nvfp4_gemm_launch(ctx->fp4, w->fp4, a_codes_dev, a_sf_dev, a_tensor_scale, M, c_bf16_dev, ctx->device,
                                    ctx->prop.multiProcessorCount, (cudaStream_t)stream, &launches, err);
     ctx->launches += launches;
     if (st) return fail(ctx, st, "%s", err.c_str());
@@ -863,5 +942,265 @@ extern "C" int32_t mpq_nvfp4_dequantize(mpq_context* ctx, int64_t R, int64_t K, 
     nvfp4_dequant_launch(codes_dev, sf_dev, tensor_scale, R, K, out_dev, (cudaStream_t)stream);
     ctx->launches += 1;
     CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_nvfp4_quantize_activations(mpq_context* ctx, const void* x_dev, int32_t x_is_bf16, int64_t M, int64_t K,
+                                                  float tensor_scale, uint8_t* codes_dev, uint8_t* sf_dev, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!x_dev || !codes_dev || !sf_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    if (M <= 0 || K <= 0 || K % 16) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 needs M > 0 and K a positive multiple of 16");
+    if (!(tensor_scale > 0.f)) return fail(ctx, MPQ_ERR_INVALID_ARG, "tensor_scale must be positive");
+    if (!aligned16(x_dev) || (reinterpret_cast<uintptr_t>(codes_dev) & 7u)) return fail(ctx, MPQ_ERR_ALIGN, "x must be 16-byte, codes 8-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    nvfp4_quantize_launch(x_dev, x_is_bf16 != 0, M, K, tensor_scale, codes_dev, sf_dev, (cudaStream_t)stream);
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// weight container: canonical arrays (interchange) and device-layout buffers (cache) on disk
+// ---------------------------------------------------------------------------
+// One file = one 128-byte header + payload.  The header carries a magic, the container version, the kind of
+// payload and, for device-layout files, the version of that layout: a file written by a build whose layout
+// differs is refused with MPQ_ERR_FORMAT and the caller rebuilds the weight from its canonical arrays -- the
+// habit of a binary cache keyed by what produced it (the reference keeps its compiled shader binaries that way:
+// platform/src/os/linux/opengl.rs:611-640, a stale or unreadable cache entry is dropped and rebuilt).
+static const uint32_t MPQ_FILE_MAGIC = 0x5751504Du;        // "MPQW"
+static const uint32_t MPQ_FILE_VERSION = 1;
+static const uint32_t MPQ_Q4_LAYOUT_VERSION = 2;           // tile stream: 1152-byte units, K padded to 4 chunks
+static const uint32_t MPQ_NVFP4_LAYOUT_VERSION = 2;        // canonical codes + scale factors tiled for 224-row tiles
+
+struct FileHeader {                                        // 128 bytes, little endian
+    uint32_t magic, version, kind, fmt;
+    uint32_t layout_version, reserved0;
+    int64_t N, K;
+    int64_t bytes_a, bytes_b;                              // canonical: codes, scales; device: stream / codes, tiled scales
+    uint64_t checksum;                                     // FNV-1a 64 over the payload
+    float tensor_scale;
+    int32_t nrp, nchunks, reserved1;
+    uint8_t pad[128 - 80];
+};
+static_assert(sizeof(FileHeader) == 128, "container header is 128 bytes");
+
+static uint64_t fnv1a64(const uint8_t* p, size_t n, uint64_t h = 0xCBF29CE484222325ull)
+{
+    for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 0x100000001B3ull; }
+    return h;
+}
+
+static int32_t file_write(const char* path, FileHeader& h, const void* a, const void* b)
+{
+    h.checksum = fnv1a64(static_cast<const uint8_t*>(b), (size_t)h.bytes_b, fnv1a64(static_cast<const uint8_t*>(a), (size_t)h.bytes_a));
+    FILE* f = fopen(path, "wb");
+    if (!f) return MPQ_ERR_IO;
+    bool ok = fwrite(&h, sizeof h, 1, f) == 1 && (h.bytes_a == 0 || fwrite(a, (size_t)h.bytes_a, 1, f) == 1) &&
+              (h.bytes_b == 0 || fwrite(b, (size_t)h.bytes_b, 1, f) == 1);
+    ok = (fclose(f) == 0) && ok;
+    return ok ? MPQ_OK : MPQ_ERR_IO;
+}
+
+// reads and validates the header; on success the file is positioned at the payload
+static int32_t file_open(const char* path, FileHeader* h, FILE** out)
+{
+    *out = nullptr;
+    FILE* f = fopen(path, "rb");
+    if (!f) return MPQ_ERR_IO;
+    if (fread(h, sizeof *h, 1, f) != 1 || h->magic != MPQ_FILE_MAGIC || h->version != MPQ_FILE_VERSION ||
+        (h->fmt != MPQ_FMT_Q4 && h->fmt != MPQ_FMT_NVFP4) || (h->kind != MPQ_FILE_CANONICAL && h->kind != MPQ_FILE_DEVICE) ||
+        h->N <= 0 || h->K <= 0 || h->bytes_a < 0 || h->bytes_b < 0 || h->bytes_a > (1LL << 40) || h->bytes_b > (1LL << 40)) {
+        fclose(f);
+        return MPQ_ERR_FORMAT;
+    }
+    if (fseek(f, 0, SEEK_END) != 0 || ftell(f) != (long)(sizeof *h + h->bytes_a + h->bytes_b) || fseek(f, sizeof *h, SEEK_SET) != 0) {
+        fclose(f);
+        return MPQ_ERR_FORMAT;                             // truncated or padded
+    }
+    *out = f;
+    return MPQ_OK;
+}
+
+static int32_t file_read_payload(FILE* f, const FileHeader& h, void* a, void* b)
+{
+    bool ok = (h.bytes_a == 0 || fread(a, (size_t)h.bytes_a, 1, f) == 1) && (h.bytes_b == 0 || fread(b, (size_t)h.bytes_b, 1, f) == 1);
+    fclose(f);
+    if (!ok) return MPQ_ERR_IO;
+    uint64_t c = fnv1a64(static_cast<const uint8_t*>(b), (size_t)h.bytes_b, fnv1a64(static_cast<const uint8_t*>(a), (size_t)h.bytes_a));
+    return c == h.checksum ? MPQ_OK : MPQ_ERR_FORMAT;
+}
+
+extern "C" int32_t mpq_file_info(const char* path, mpq_file_info_t* out)
+{
+    if (!path || !out) return MPQ_ERR_INVALID_ARG;
+    FileHeader h;
+    FILE* f;
+    int32_t st = file_open(path, &h, &f);
+    if (st) return st;
+    fclose(f);
+    out->kind = (int32_t)h.kind; out->fmt = (int32_t)h.fmt; out->layout_version = (int32_t)h.layout_version;
+    out->N = h.N; out->K = h.K; out->bytes_a = h.bytes_a; out->bytes_b = h.bytes_b; out->tensor_scale = h.tensor_scale;
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_canonical_save(const char* path, int32_t fmt, int64_t N, int64_t K, const uint8_t* codes_host,
+                                      const void* scales_host, float tensor_scale)
+{
+    if (!path || !codes_host || !scales_host) return MPQ_ERR_INVALID_ARG;
+    if (fmt != MPQ_FMT_Q4 && fmt != MPQ_FMT_NVFP4) return MPQ_ERR_INVALID_ARG;
+    if (N <= 0 || K <= 0 || K % (fmt == MPQ_FMT_Q4 ? 32 : 16)) return MPQ_ERR_SHAPE;
+    FileHeader h = {};
+    h.magic = MPQ_FILE_MAGIC; h.version = MPQ_FILE_VERSION; h.kind = MPQ_FILE_CANONICAL; h.fmt = (uint32_t)fmt;
+    h.N = N; h.K = K; h.tensor_scale = fmt == MPQ_FMT_Q4 ? 1.f : tensor_scale;
+    h.bytes_a = N * (K / 2);
+    h.bytes_b = fmt == MPQ_FMT_Q4 ? N * (K / 32) * 2 : N * (K / 16);
+    return file_write(path, h, codes_host, scales_host);
+}
+
+extern "C" int32_t mpq_canonical_load(const char* path, uint8_t* codes_host, int64_t codes_capacity, void* scales_host,
+                                      int64_t scales_capacity, float* tensor_scale)
+{
+    if (!path || !codes_host || !scales_host) return MPQ_ERR_INVALID_ARG;
+    FileHeader h;
+    FILE* f;
+    int32_t st = file_open(path, &h, &f);
+    if (st) return st;
+    if (h.kind != MPQ_FILE_CANONICAL) { fclose(f); return MPQ_ERR_FORMAT; }
+    if (h.bytes_a > codes_capacity || h.bytes_b > scales_capacity) { fclose(f); return MPQ_ERR_SHAPE; }
+    if (tensor_scale) *tensor_scale = h.tensor_scale;
+    return file_read_payload(f, h, codes_host, scales_host);
+}
+
+extern "C" int32_t mpq_weight_save(mpq_context* ctx, const mpq_weight* w, const char* path)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!w_ok(w) || !path) return fail(ctx, MPQ_ERR_INVALID_ARG, "null or stale handle / path");
+    if (w->device != ctx->device) return fail(ctx, MPQ_ERR_INVALID_ARG, "weight lives on device %d, context on %d", w->device, ctx->device);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    FileHeader h = {};
+    h.magic = MPQ_FILE_MAGIC; h.version = MPQ_FILE_VERSION; h.kind = MPQ_FILE_DEVICE; h.fmt = (uint32_t)w->fmt;
+    const void *da, *db;
+    if (w->fmt == MPQ_FMT_Q4) {
+        h.layout_version = MPQ_Q4_LAYOUT_VERSION;
+        h.N = w->q4.N; h.K = w->q4.K; h.nrp = w->q4.nrp; h.nchunks = w->q4.nchunks; h.tensor_scale = 1.f;
+        h.bytes_a = (int64_t)w->q4.bytes(); h.bytes_b = 0;
+        da = w->q4.stream; db = nullptr;
+    } else {
+        h.layout_version = MPQ_NVFP4_LAYOUT_VERSION;
+        h.N = w->fp4.N; h.K = w->fp4.K; h.tensor_scale = w->fp4.tensor_scale;
+        h.bytes_a = w->fp4.N * (w->fp4.K / 2); h.bytes_b = (int64_t)w->fp4.sf_tiled_bytes;
+        da = w->fp4.codes; db = w->fp4.sf_tiled;
+    }
+    uint8_t* host = static_cast<uint8_t*>(malloc((size_t)(h.bytes_a + h.bytes_b) + 1));
+    if (!host) return fail(ctx, MPQ_ERR_CUDA, "out of host memory");
+    cudaError_t e = cudaMemcpy(host, da, (size_t)h.bytes_a, cudaMemcpyDeviceToHost);        // synchronises with prior work
+    if (e == cudaSuccess && h.bytes_b) e = cudaMemcpy(host + h.bytes_a, db, (size_t)h.bytes_b, cudaMemcpyDeviceToHost);
+    int32_t st = e == cudaSuccess ? file_write(path, h, host, host + h.bytes_a) : MPQ_ERR_CUDA;
+    free(host);
+    if (st == MPQ_ERR_CUDA) return fail(ctx, st, "device-to-host copy failed: %s", cudaGetErrorString(e));
+    if (st) return fail(ctx, st, "cannot write %s", path);
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_weight_load(mpq_context* ctx, const char* path, mpq_weight** out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!path || !out) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    *out = nullptr;
+    FileHeader h;
+    FILE* f;
+    int32_t st = file_open(path, &h, &f);
+    if (st) return fail(ctx, st, "%s: %s", path, st == MPQ_ERR_IO ? "cannot open" : "not a weight container of this version");
+    // geometry the current layout would give this shape: anything else was written by another layout
+    bool fits = h.kind == MPQ_FILE_DEVICE;
+    if (fits && h.fmt == MPQ_FMT_Q4) {
+        Q4Dev q;
+        q.nrp = (int)((h.N + 31) / 32);
+        q.nchunks = (int)((h.K + 63) / 64);
+        q.nchunks = (q.nchunks + Q4_GROUP_PAD - 1) / Q4_GROUP_PAD * Q4_GROUP_PAD;
+        fits = h.layout_version == MPQ_Q4_LAYOUT_VERSION && h.K % 32 == 0 && h.nrp == q.nrp && h.nchunks == q.nchunks &&
+               h.bytes_a == (int64_t)q.bytes() && h.bytes_b == 0;
+    } else if (fits) {
+        fits = h.layout_version == MPQ_NVFP4_LAYOUT_VERSION && h.K % 32 == 0 && h.N % 8 == 0 && h.bytes_a == h.N * (h.K / 2) &&
+               h.bytes_b == (int64_t)nvfp4_sf_tiled_bytes(h.N, h.K);
+    }
+    if (!fits) {
+        fclose(f);
+        return fail(ctx, MPQ_ERR_FORMAT, "%s: device layout of another build (rebuild the weight from its canonical arrays)", path);
+    }
+    uint8_t* host = static_cast<uint8_t*>(malloc((size_t)(h.bytes_a + h.bytes_b) + 1));
+    if (!host) { fclose(f); return fail(ctx, MPQ_ERR_CUDA, "out of host memory"); }
+    st = file_read_payload(f, h, host, host + h.bytes_a);
+    if (st) { free(host); return fail(ctx, st, "%s: %s", path, st == MPQ_ERR_IO ? "read failed" : "checksum mismatch"); }
+    cudaError_t e = cudaSetDevice(ctx->device);
+    mpq_weight* w = new (std::nothrow) mpq_weight();
+    if (!w) { free(host); return fail(ctx, MPQ_ERR_CUDA, "out of host memory"); }
+    w->magic = W_MAGIC; w->fmt = (int)h.fmt; w->device = ctx->device;
+    if (h.fmt == MPQ_FMT_Q4) {
+        w->q4.N = h.N; w->q4.K = h.K; w->q4.nrp = h.nrp; w->q4.nchunks = h.nchunks;
+        if (e == cudaSuccess) e = cudaMalloc(&w->q4.stream, (size_t)h.bytes_a);
+        if (e == cudaSuccess) e = cudaMemcpy(w->q4.stream, host, (size_t)h.bytes_a, cudaMemcpyHostToDevice);
+    } else {
+        w->fp4.N = h.N; w->fp4.K = h.K; w->fp4.tensor_scale = h.tensor_scale; w->fp4.sf_tiled_bytes = (size_t)h.bytes_b;
+        if (e == cudaSuccess) e = cudaMalloc(&w->fp4.codes, (size_t)h.bytes_a);
+        if (e == cudaSuccess) e = cudaMalloc(&w->fp4.sf_tiled, (size_t)h.bytes_b);
+        if (e == cudaSuccess) e = cudaMemcpy(w->fp4.codes, host, (size_t)h.bytes_a, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(w->fp4.sf_tiled, host + h.bytes_a, (size_t)h.bytes_b, cudaMemcpyHostToDevice);
+    }
+    free(host);
+    if (e != cudaSuccess) {
+        cudaFree(w->q4.stream);
+        w->fp4.release();
+        delete w;
+        return fail(ctx, MPQ_ERR_CUDA, "upload of %s failed: %s", path, cudaGetErrorString(e));
+    }
+    *out = w;
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
+// measured ceilings (what the roofline fractions are quoted against)
+// ---------------------------------------------------------------------------
+// Read-only HBM streaming: every thread sums 16-byte words with the same no-allocate loads the kernels use.
+__global__ void __launch_bounds__(512) hbm_read_probe_kernel(const uint4* __restrict__ src, int64_t n16, uint32_t* __restrict__ out)
+{
+    uint32_t acc = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n16; i += 4 * stride) {        // four loads in flight per thread
+        uint4 a = ldg_stream(src + i), b = ldg_stream(src + i + stride), c = ldg_stream(src + i + 2 * stride), d = ldg_stream(src + i + 3 * stride);
+        acc += (a.x ^ a.y ^ a.z ^ a.w) + (b.x ^ b.y ^ b.z ^ b.w) + (c.x ^ c.y ^ c.z ^ c.w) + (d.x ^ d.y ^ d.z ^ d.w);
+    }
+    for (; i < n16; i += stride) {
+        uint4 a = ldg_stream(src + i);
+        acc += a.x ^ a.y ^ a.z ^ a.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if ((threadIdx.x & 31) == 0 && acc == 0x9E3779B9u) atomicAdd(out, 1u);     // keeps the loads alive; practically never taken
+}
+
+extern "C" int32_t mpq_probe_hbm_read(mpq_context* ctx, const void* buf_dev, int64_t bytes, uint32_t* out_dev, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!buf_dev || !out_dev || bytes < 16) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer or empty buffer");
+    if (!aligned16(buf_dev)) return fail(ctx, MPQ_ERR_ALIGN, "buffer must be 16-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    hbm_read_probe_kernel<<<ctx->prop.multiProcessorCount * 4, 512, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(buf_dev), bytes / 16, out_dev);
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_probe_fp4_mma(mpq_context* ctx, int32_t mmas_per_sm, double* flop_out, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (mmas_per_sm <= 0 || mmas_per_sm > (1 << 24)) return fail(ctx, MPQ_ERR_INVALID_ARG, "mmas_per_sm=%d out of range", mmas_per_sm);
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    std::string err;
+    int32_t st = nvfp4_mma_probe_launch(ctx->fp4, ctx->device, ctx->prop.multiProcessorCount, mmas_per_sm, (cudaStream_t)stream, flop_out, err);
+    ctx->launches += 1;
+    if (st) return fail(ctx, st, "%s", err.c_str());
     return MPQ_OK;
 }

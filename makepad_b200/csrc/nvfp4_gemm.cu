@@ -32,6 +32,7 @@
 #include <cstdlib>
 
 #include "nvfp4.cuh"
+#include "per_device.h"
 
 namespace mpq {
 
@@ -78,9 +79,120 @@ void nvfp4_dequant_launch(const uint8_t* codes, const uint8_t* sf, float ts, int
 }
 
 // ---------------------------------------------------------------------------
+// activation quantisation: fp32 / bf16 rows -> canonical NVFP4 (what the GEMM takes as A)
+// ---------------------------------------------------------------------------
+// Per row and 16-element block: amax = max |x|; scale byte = e4m3(amax / (6 * ts)), round to nearest even,
+// saturating at 448; each element -> e2m1(x / (e4m3 value * ts)), round to nearest even, saturating at 6; a block
+// whose scale encodes to zero gets all-zero codes.  binary32 arithmetic with correctly rounded divisions, so the
+// result is the same bit pattern on any IEEE machine.  One thread per block: 64 (32) bytes in, 9 bytes out.
+__device__ __forceinline__ uint32_t f32_to_e4m3_sat(float x)          // x >= 0, finite
+{
+    if (x >= 448.f) return 0x7Eu;
+    // grid spacing 2^-9 below 2^-6, else 2^(floor(log2 x) - 3)
+    int le = (int)((__float_as_uint(x) >> 23) & 0xFFu) - 127;
+    if (le < -6) le = -6;
+    const float q = __uint_as_float((uint32_t)(le - 3 + 127) << 23);
+    const float y = rintf(__fdiv_rn(x, q)) * q;                        // exact: q is a power of two
+    if (y == 0.f) return 0u;
+    const int yle = (int)((__float_as_uint(y) >> 23) & 0xFFu) - 127;
+    if (yle < -6) return (uint32_t)(y * 512.f);                        // subnormal: mantissa count of 2^-9
+    const uint32_t man = (uint32_t)(y * __uint_as_float((uint32_t)(3 - yle + 127) << 23)) - 8u;
+    return ((uint32_t)(yle + 7) << 3) | man;
+}
+
+__device__ __forceinline__ uint32_t f32_to_e2m1_sat(float f)
+{
+    const uint32_t sign = (__float_as_uint(f) >> 31) ? 8u : 0u;
+    const float x = fabsf(f);
+    uint32_t m;
+    if (x <= 0.25f) m = 0;
+    else if (x < 0.75f) m = 1;
+    else if (x <= 1.25f) m = 2;
+    else if (x < 1.75f) m = 3;
+    else if (x <= 2.5f) m = 4;
+    else if (x < 3.5f) m = 5;
+    else if (x <= 5.0f) m = 6;
+    else m = 7;
+    return sign | m;
+}
+
+template <bool BF16>
+__global__ void nvfp4_quantize_kernel(const void* __restrict__ xin, int64_t R, int64_t K, float ts, uint8_t* __restrict__ codes,
+                                      uint8_t* __restrict__ sf)
+{
+    const int64_t blk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (blk >= R * (K / 16)) return;
+    float v[16];
+    if (BF16) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(xin) + blk * 16);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const uint4 u = src[q];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[8 * q + 2 * i] = __uint_as_float(w[i] << 16);
+                v[8 * q + 2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+        }
+    } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(xin) + blk * 16);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 f = src[q];
+            v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+        }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const uint32_t s8 = f32_to_e4m3_sat(__fdiv_rn(amax, 6.0f * ts));
+    const float d = e4m3_value(s8) * ts;
+    uint32_t lo = 0, hi = 0;
+    if (d > 0.f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            lo |= f32_to_e2m1_sat(__fdiv_rn(v[i], d)) << (4 * i);
+            hi |= f32_to_e2m1_sat(__fdiv_rn(v[8 + i], d)) << (4 * i);
+        }
+    }
+    reinterpret_cast<uint2*>(codes)[blk] = make_uint2(lo, hi);          // element 2j in the low nibble of byte j
+    sf[blk] = (uint8_t)s8;
+}
+
+void nvfp4_quantize_launch(const void* x, bool bf16, int64_t R, int64_t K, float ts, uint8_t* codes, uint8_t* sf, cudaStream_t s)
+{
+    const int64_t blocks = R * (K / 16);
+    const unsigned grid = (unsigned)((blocks + 255) / 256);
+    if (bf16) nvfp4_quantize_kernel<true><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+    else nvfp4_quantize_kernel<false><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+}
+
+// ---------------------------------------------------------------------------
 // geometry
 // ---------------------------------------------------------------------------
 constexpr int BM = 128, BN = 224, BK = 256;               // BK in elements
+
+// The same export for a WEIGHT, whose scale factors exist on the device only in the tiled order the GEMM
+// consumes (nvfp4_sf_tile_kernel with tiles of BN rows): reading them back from there proves the tiling pass.
+__global__ void nvfp4_dequant_tiled_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf_tiled, float ts,
+                                           int64_t R, int64_t K, int ksteps_pad, float* __restrict__ out)
+{
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t total = R * (K / 2);
+    if (i >= total) return;
+    int64_t r = i / (K / 2), kb = i - r * (K / 2);
+    uint32_t b = codes[i];
+    const int atoms = (BN + 127) / 128;
+    int64_t tile = r / BN;
+    int local = (int)(r - tile * BN), atom = local >> 7, lrow = local & 127;
+    int64_t kstep = kb >> 5;                                  // 64 elements = 32 bytes of codes per K step
+    int j = (int)((kb >> 3) & 3);                             // which of the step's four scales
+    size_t off = (((size_t)tile * ksteps_pad + kstep) * atoms + atom) * 512 + (lrow & 31) * 16 + (lrow >> 5) * 4 + j;
+    float s = e4m3_value(sf_tiled[off]);
+    out[r * K + 2 * kb] = e2m1_value(b & 0xF) * s * ts;
+    out[r * K + 2 * kb + 1] = e2m1_value(b >> 4) * s * ts;
+}
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK / 2;                       // 16384
 constexpr int B_BYTES = BN * BK / 2;                       // 28672
@@ -123,6 +235,13 @@ __global__ void nvfp4_sf_tile_kernel(const uint8_t* __restrict__ sf, int64_t row
 
 static inline int ksteps_padded(int64_t K) { return (int)(((K + 63) / 64 + 3) / 4 * 4); }
 
+void nvfp4_weight_dequant_launch(const Nvfp4Dev& w, float* out, cudaStream_t s)
+{
+    int64_t total = w.N * (w.K / 2);
+    nvfp4_dequant_tiled_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(w.codes, w.sf_tiled, w.tensor_scale, w.N, w.K,
+                                                                                 ksteps_padded(w.K), out);
+}
+
 // tile_multiple: the number of tiles is rounded up to a multiple of it (2 for the activations: a CTA pair always
 // loads two 128-row slabs); the extra tiles are zero
 static cudaError_t sf_tile_launch(const uint8_t* sf, int64_t rows, int64_t K, int tile_rows, uint8_t* dst, cudaStream_t s, int tile_multiple = 1)
@@ -144,18 +263,23 @@ static size_t sf_tiled_bytes(int64_t rows, int64_t K, int tile_rows, int tile_mu
     return (size_t)tiles * ksteps_padded(K) * atoms * 512;
 }
 
+size_t nvfp4_sf_tiled_bytes(int64_t N, int64_t K) { return sf_tiled_bytes(N, K, BN); }
+
 int32_t nvfp4_weight_build(Nvfp4Dev& w, int64_t N, int64_t K, const uint8_t* codes_host, const uint8_t* sf_host, float ts,
                            int* launches, std::string& err)
 {
     w.N = N; w.K = K; w.tensor_scale = ts;
     size_t cb = (size_t)N * (K / 2), sb = (size_t)N * (K / 16);
+    uint8_t* sf_canonical = nullptr;                      // staging only: the device keeps the tiled copy
+    w.sf_tiled_bytes = sf_tiled_bytes(N, K, BN);
     cudaError_t e = cudaMalloc(&w.codes, cb);
-    if (e == cudaSuccess) e = cudaMalloc(&w.sf_canonical, sb);
-    if (e == cudaSuccess) e = cudaMalloc(&w.sf_tiled, sf_tiled_bytes(N, K, BN));
+    if (e == cudaSuccess) e = cudaMalloc(&sf_canonical, sb);
+    if (e == cudaSuccess) e = cudaMalloc(&w.sf_tiled, w.sf_tiled_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(w.codes, codes_host, cb, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(w.sf_canonical, sf_host, sb, cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = sf_tile_launch(w.sf_canonical, N, K, BN, w.sf_tiled, 0);
+    if (e == cudaSuccess) e = cudaMemcpy(sf_canonical, sf_host, sb, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = sf_tile_launch(sf_canonical, N, K, BN, w.sf_tiled, 0);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    cudaFree(sf_canonical);
     *launches = 1;
     if (e != cudaSuccess) { err = std::string("NVFP4 weight build failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
     return MPQ_OK;
@@ -850,6 +974,89 @@ nvfp4_gemm_pair_kernel_v2(const __grid_constant__ CUtensorMap map_a, const __gri
 }
 
 // ---------------------------------------------------------------------------
+// measured ceiling of the FP4 tensor pipe
+// ---------------------------------------------------------------------------
+// One CTA per SM issues `mmas` block-scaled FP4 MMAs of the GEMM's own shape (128 x 224 x 64, operands in shared
+// memory, scale factors in TMEM) back to back, with no loads, no hand-offs and one commit at the end: what the
+// tensor pipe sustains when nothing else is in its way.  2 * 128 * 224 * 64 flop per MMA and CTA.
+__global__ void __launch_bounds__(128, 1) nvfp4_mma_probe_kernel(int mmas, int* status)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    const uint32_t smem0 = (s2u(smem_dyn) + 1023u) & ~1023u;
+    const uint32_t bar = smem0 + A_BYTES + B_BYTES;
+    const int warp = threadIdx.x >> 5;
+    // operands: every byte 0x22 (two e2m1 codes of value 1.0); any bit pattern is a valid operand
+    for (uint32_t i = threadIdx.x * 16; i < (uint32_t)(A_BYTES + B_BYTES); i += blockDim.x * 16)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem0 + i), "r"(0x22222222u) : "memory");
+    if (threadIdx.x == 0) {
+        bar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s2u(&s_tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    {   // scale factors 1.0 (e4m3 0x38) in 48 columns beside the accumulator, every lane quarter its own copy
+        uint32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0x38383838u;
+        const uint32_t dst = tmem + ((uint32_t)(warp * 32) << 16) + V2_SF_COL;
+        tc_st16(dst, r); tc_st16(dst + 16, r); tc_st16(dst + 32, r);
+        tc_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+        const uint64_t adesc = smem_desc_sw128(smem0), bdesc = smem_desc_sw128(smem0 + A_BYTES);
+        const uint32_t sfb_c = tmem + V2_SF_COL, sfa_c = sfb_c + 32;
+        for (int i = 0; i < mmas; i += 4) {
+            tc_mma_nvf4(tmem, adesc, bdesc, idesc, sfa_c, sfb_c, i ? 1u : 0u);
+            tc_mma_nvf4(tmem, adesc + 2, bdesc + 2, idesc, sfa_c + 4, sfb_c + 8, 1u);
+            tc_mma_nvf4(tmem, adesc + 4, bdesc + 4, idesc, sfa_c + 8, sfb_c + 16, 1u);
+            tc_mma_nvf4(tmem, adesc + 6, bdesc + 6, idesc, sfa_c + 12, sfb_c + 24, 1u);
+        }
+        tc_commit(bar);
+        if (!bar_wait(bar, 0u, SPIN_LIMIT)) atomicExch(status, 21);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+int32_t nvfp4_mma_probe_launch(Nvfp4Scratch& scratch, int device, int sm_count, int mmas, cudaStream_t s, double* flop, std::string& err)
+{
+    if (!scratch.status) {
+        cudaError_t e = cudaMalloc(&scratch.status, sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(scratch.status, 0, sizeof(int));
+        if (e != cudaSuccess) { err = std::string("status allocation failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    }
+    const int smem = A_BYTES + B_BYTES + 1024 + 64;
+    static PerDeviceOnce configured;
+    if (configured.needs(device)) {
+        cudaError_t e = cudaFuncSetAttribute(nvfp4_mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+        configured.mark(device);
+    }
+    mmas = (mmas + 3) / 4 * 4;
+    nvfp4_mma_probe_kernel<<<sm_count, 128, smem, s>>>(mmas, scratch.status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { err = std::string("nvfp4_mma_probe_kernel launch failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
+    if (flop) *flop = 2.0 * BM * BN * 64 * (double)mmas * sm_count;
+    return MPQ_OK;
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -910,10 +1117,13 @@ static bool make_c_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int b
 
 // CTA pairs the device can keep resident at once (0: the pair kernel cannot be used)
 
-static int pair_v2_clusters(int sm_count)
+static int pair_v2_clusters(int device, int sm_count)
 {
-    static int cached = -1;
-    if (cached >= 0) return cached;
+    static int cached_n[PerDeviceOnce::MAX_DEVICES];      // per device: the attribute and the occupancy both are
+    static PerDeviceOnce known;
+    if (!known.needs(device)) return cached_n[device];
+    int& cached = (device >= 0 && device < PerDeviceOnce::MAX_DEVICES) ? cached_n[device] : cached_n[0];
+    known.mark(device);
     cached = 0;
     if (cudaFuncSetAttribute(nvfp4_gemm_pair_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
     cudaLaunchConfig_t cfg = {};
@@ -932,7 +1142,7 @@ static int pair_v2_clusters(int sm_count)
 }
 
 int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_t* a_codes, const uint8_t* a_sf, float ta,
-                          int64_t M, uint16_t* c, int sm_count, cudaStream_t s, int* launches, std::string& err)
+                          int64_t M, uint16_t* c, int device, int sm_count, cudaStream_t s, int* launches, std::string& err)
 {
     *launches = 0;
     const int64_t N = w.N, K = w.K;
@@ -969,7 +1179,7 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     // CTA pairs where clusters of two can be scheduled (MPQ_FP4_KERNEL=single forces the one-CTA kernel, which the
     // parity tests use to cover both)
     const char* env = getenv("MPQ_FP4_KERNEL");
-    const int nclusters = (env && std::string(env) == "single") ? 0 : pair_v2_clusters(sm_count);
+    const int nclusters = (env && std::string(env) == "single") ? 0 : pair_v2_clusters(device, sm_count);
     if (nclusters > 0) {
         CUtensorMap map_bh, map_c;
         if (!make_map(&map_bh, w.codes, N, K, BN / 2) || !make_c_map(&map_c, c, M, N, Q_OUT_COLS)) { err = "cuTensorMapEncodeTiled failed for the CTA-pair kernel"; return MPQ_ERR_CUDA; }
@@ -998,11 +1208,11 @@ int32_t nvfp4_gemm_launch(Nvfp4Scratch& scratch, const Nvfp4Dev& w, const uint8_
     p.scale = ta * w.tensor_scale;
     p.status = scratch.status;
     p.sfa_direct = direct ? 1 : 0;
-    static bool configured = false;
-    if (!configured) {
+    static PerDeviceOnce configured;
+    if (configured.needs(device)) {
         e = cudaFuncSetAttribute(nvfp4_gemm_kernel_v2, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) { err = std::string("cudaFuncSetAttribute failed: ") + cudaGetErrorString(e); return MPQ_ERR_CUDA; }
-        configured = true;
+        configured.mark(device);
     }
     int grid = std::min(sm_count, p.m_tiles * p.n_tiles);
     nvfp4_gemm_kernel_v2<<<grid, V2_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_sfa, map_c1, p);

@@ -51,9 +51,9 @@ struct Q4Dev {
 constexpr int Q4_UNIT_BYTES = 1152;
 constexpr int Q4_UNIT_U4 = Q4_UNIT_BYTES / 16;   // 72 uint4 per unit: 32 + 32 codes, 8 scales
 
-constexpr int Q4_WARPS = 8;
+constexpr int Q4_WARPS = 8;     // warps per CTA of the phase-staged kernel (q4_linear_kernel)
 constexpr int Q4_THREADS = Q4_WARPS * 32;
-constexpr int Q4_PF = 4;       // chunk loads in flight per warp
+constexpr int Q4_PF = 4;       // chunk loads in flight per warp of that kernel
 
 // ---------------------------------------------------------------------------
 // repack: canonical -> tile stream.  One thread per 32-bit code word.
@@ -432,14 +432,22 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // ---------------------------------------------------------------------------
 // the streaming kernel: M <= 4, whole x resident in shared memory
 // ---------------------------------------------------------------------------
-// One CTA of sixteen warps per SM, no CTA-wide synchronisation between staging
-// the activation and draining the runs.  The unit stream is cut into contiguous
-// runs of GROUPS (G consecutive chunks of one row pair-tile; the layout pads K
-// so that a group never straddles a tile), one run per warp.  When the matrix
-// has at least about one row pair-tile per SM, each CTA takes WHOLE tiles and
-// its warps split them, so no tile is shared between CTAs; otherwise (few
-// rows, e.g. a tensor-parallel shard) all warps of the grid take equal runs and
-// tiles cut by a CTA boundary are finished through global scratch.  Each warp owns a private ring of
+// One CTA of sixteen warps per SM and launch, no CTA-wide synchronisation
+// between staging the activation and draining the runs.  Where the activation
+// is short enough the kernel is built for 64 registers per thread and asks for
+// less than half of an SM's shared memory, so that the CTA of the NEXT launch
+// in the stream (programmatic dependent launch) is resident beside this one:
+// its start-up, barrier initialisation and the bulk copies that fill its ring
+// all run while this launch still streams, and only what depends on the
+// activation is left after griddepcontrol.wait.
+//
+// The unit stream is cut into contiguous runs of GROUPS (G consecutive chunks
+// of one row pair-tile; the layout pads K so that a group never straddles a
+// tile), one run per warp.  When the matrix has at least about one row
+// pair-tile per SM, each CTA takes WHOLE tiles and its warps split them, so no
+// tile is shared between CTAs; otherwise (few rows, e.g. a tensor-parallel
+// shard) all warps of the grid take equal runs and tiles cut by a CTA boundary
+// are finished through global scratch.  Each warp owns a private ring of
 // shared-memory stages that its lane 0 keeps full with cp.async.bulk copies
 // (mbarrier complete_tx), so the HBM stream of a warp never waits for its
 // arithmetic and -- because the first copies are issued BEFORE
@@ -448,10 +456,12 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // to y.  A tile shared by warps of one CTA is summed through shared memory, in
 // warp order, when the CTA has drained its runs.  A tile cut by the boundary
 // between two CTAs is finished through global scratch (q4s_cross_cta).
-constexpr int Q4S_WARPS = 16;                   // one CTA of sixteen warps per SM
-constexpr int Q4S_THREADS = Q4S_WARPS * 32;
+constexpr int Q4S_WARPS_FULL = 16;               // warps of a CTA that has an SM to itself
+constexpr int Q4S_WARPS_HALF = 12;               // warps of a CTA that shares an SM with the next launch's (85 registers each)
+constexpr int Q4S_MAX_DEPTH = 8;                 // most ring stages per warp
 constexpr int Q4_GROUP_PAD = 4;                  // chunks per row pair-tile are padded to a multiple of this
 constexpr uint32_t Q4S_SPIN_LIMIT = 1u << 22;    // polls of one mbarrier before giving up
+constexpr size_t Q4S_SLOT_BYTES_PER_CTA = 2 * 32 * 4 * sizeof(uint2);   // two tagged partial tiles per CTA
 
 struct Q4StreamLaunch {
     const uint4* stream;
@@ -461,10 +471,10 @@ struct Q4StreamLaunch {
     int64_t ldy;
     int nchunks;            // per row pair-tile, a multiple of G
     int groups;             // nrp * nchunks / G
-    int warps_total;        // W: warps that own a run (<= 16*gridDim.x, <= groups); split mode only
+    int warps_total;        // W: warps that own a run (<= NW*gridDim.x, <= groups); split mode only
     int tile_mode;          // 1: CTA b owns row pair-tiles [b*nrp/grid, (b+1)*nrp/grid) and its warps split them
     int nrp;                // row pair-tiles
-    int depth;              // ring stages per warp
+    int depth;              // ring stages per warp (<= Q4S_MAX_DEPTH)
     int pre;                // stages copied before the dependency on the previous kernel resolves (the rest after the activation loads)
     uint2* partials;        // [CTAs][2][32 lanes][4] (value, tag) pairs
     int* status;            // set non-zero when a bounded wait ran out
@@ -476,9 +486,31 @@ struct Q4StreamLaunch {
     uint2* xpeer[8];        // rank r's exchange buffer (this rank's own for r == xrank), already offset to this launch's half
     int64_t xslot;          // uint2 per slot (>= M * N)
     uint32_t xlimit;        // polls of one element before giving up
+#ifdef MPQ_TRACE
+    unsigned long long* trace;   // [CTAs][8] %globaltimer stamps of thread 0 (diagnostic build only)
+#endif
 };
 
+// Diagnostic build (-DMPQ_TRACE): thread 0 of every CTA records when it passed each phase of the kernel.
+#ifdef MPQ_TRACE
+#define Q4S_TRACE(slot)                                                        \
+    if (p.trace && tid == 0) {                                                 \
+        unsigned long long t_;                                                 \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                 \
+        p.trace[(size_t)blockIdx.x * 8 + (slot)] = t_;                         \
+    }
+#else
+#define Q4S_TRACE(slot)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// 16-byte load from a 32-bit shared-memory address (half the address registers of a generic pointer)
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count)
 {
@@ -543,29 +575,32 @@ __device__ __forceinline__ int q4s_owner(int gidx, int groups, int W)
     return i;
 }
 
+// A (value, tag) pair travels as ONE 64-bit access: single-copy atomic under the PTX memory model, so a
+// reader that sees the tag sees the value.  (A .v2.u32 access would be two scalar accesses of unspecified order.)
+__device__ __forceinline__ uint64_t pack_tagged(float v, uint32_t tag) { return ((uint64_t)tag << 32) | __float_as_uint(v); }
+__device__ __forceinline__ uint2 unpack_tagged(uint64_t w) { return make_uint2((uint32_t)w, (uint32_t)(w >> 32)); }
 __device__ __forceinline__ void st_tagged(uint2* p, float v, uint32_t tag)
 {
-    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(pack_tagged(v, tag)) : "memory");
 }
 __device__ __forceinline__ uint2 ld_tagged(const uint2* p)
 {
-    uint2 r;
-    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-    return r;
+    uint64_t w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return unpack_tagged(w);
 }
-
-// Write one finished row pair-tile to y.  v[tile*2+h] belongs to row tile*16 + g + 8h, activation row t.
 __device__ __forceinline__ void st_tagged_sys(uint2* p, float v, uint32_t tag)
 {
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(pack_tagged(v, tag)) : "memory");
 }
 __device__ __forceinline__ uint2 ld_tagged_sys(const uint2* p)
 {
-    uint2 r;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p) : "memory");
-    return r;
+    uint64_t w;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return unpack_tagged(w);
 }
 
+// Write one finished row pair-tile to y.  v[tile*2+h] belongs to row tile*16 + g + 8h, activation row t.
 __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const float (&v)[4], int rp, int lane)
 {
     const int g = lane >> 2, t = lane & 3;
@@ -592,19 +627,20 @@ __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const fl
 // the sum does not depend on timing, writes y, and clears the slots it consumed.  A slot is written
 // once and read once per launch, and the next launch writes only after this one has completed, so the
 // protocol needs no per-launch state (it is safe under CUDA-graph replay).
+template <int NW>
 __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float v0, float v1, float v2, float v3, int rp, int r0,
                                            int r1, int cta_first_rp, int lane)
 {
     float v[4] = {v0, v1, v2, v3};
     const int W = p.warps_total;
-    const int c0 = q4s_owner(r0, p.groups, W) / Q4S_WARPS;
+    const int c0 = q4s_owner(r0, p.groups, W) / NW;
     if ((int)blockIdx.x != c0) {
         uint2* mine = p.partials + (((size_t)blockIdx.x * 2 + (rp == cta_first_rp ? 0 : 1)) * 32 + lane) * 4;
 #pragma unroll
         for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], 1u);
         return;
     }
-    const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4S_WARPS;
+    const int c1 = q4s_owner(r1 - 1, p.groups, W) / NW;
     // every later CTA starts its run inside this tile, so the tile is its first one (slot 0)
     const uint2* src = p.partials + (((size_t)(c0 + 1) * 2) * 32 + lane) * 4;
     for (int c = c0 + 1; c <= c1; c += 4) {                // four contributors' loads in flight at a time
@@ -637,90 +673,119 @@ __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float v0, fl
     q4s_store_tile(p, v, rp, lane);
 }
 
-// One float4 of x -> normalised hi/lo fp16 fragments in xs, block corrections in cs.
+// One float4 of x (element index 4f of activation row m) -> normalised hi/lo fp16 fragments in xs, block
+// corrections in cs.
 //   xs: uint4 [chunk][2M columns][4 t][2 blocks]   column 2m = hi, 2m+1 = lo of activation row m; the uint4 of
 //                                                  lane t holds halves [j0: k 2t,2t+1 | j0: k 2t+8,2t+9 | j1 ...]
-//   cs: float4[chunk][M][2 blocks]                 (c_hi, c_lo, 16 c_hi, 16 c_lo): the MMA's C operand
-template <bool SUBN>
-__device__ __forceinline__ void q4s_stage_one(float4 v, bool on, int m, int f, float sc, int M, int ncols, uint4* xs,
-                                              float4* cs, int lane)
+//   cs: float4[chunk][M]                           (c, 16c) of block 0, (c, 16c) of block 1, c = -8 * 2^-24 * sum of
+//                                                  the block's scaled x: the hi column's C operand (the lo column's is 0);
+//                                                  hi + lo differs from the scaled x by < 2^-22 of it, which is what the
+//                                                  sum may be off by as well
+__device__ __forceinline__ void q4s_stage_one(float4 v, bool on, int m, int f, float sc, int ncols, int M, uint4* xs, float4* cs,
+                                              int lane)
 {
-    float e[4] = {v.x * sc, v.y * sc, v.z * sc, v.w * sc};
-    __half hi[4], lo[4];
-    float shi = 0.f, slo = 0.f;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        hi[q] = __float2half_rn(e[q]);
-        float hf = __half2float(hi[q]);
-        lo[q] = __float2half_rn(e[q] - hf);
-        shi += hf;
-        slo += __half2float(lo[q]);
-    }
-    const int kk = 4 * f, chunk = kk >> 6, blk = (kk >> 5) & 1;
+    const float e0 = v.x * sc, e1 = v.y * sc, e2 = v.z * sc, e3 = v.w * sc;
+    const __half2 h01 = __floats2half2_rn(e0, e1), h23 = __floats2half2_rn(e2, e3);
+    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    const __half2 l01 = __floats2half2_rn(e0 - f01.x, e1 - f01.y), l23 = __floats2half2_rn(e2 - f23.x, e3 - f23.y);
+    float sum = (e0 + e1) + (e2 + e3);
+    const int chunk = f >> 4, r = f & 15;
+    const int blk = r >> 3, jj = (r >> 2) & 1, up = (r >> 1) & 1, tt0 = (r & 1) * 2;
     if (on) {
-        int jj = (kk >> 4) & 1, slot = kk & 15;
-        int tt0 = (slot & 7) >> 1, up = slot >> 3;
         __half2* dst = reinterpret_cast<__half2*>(xs + ((size_t)chunk * ncols + 2 * m) * 8);   // 8 uint4 per column
-        int w0 = (tt0 * 2 + blk) * 4 + jj * 2 + up, w1 = ((tt0 + 1) * 2 + blk) * 4 + jj * 2 + up;
-        dst[w0] = __halves2half2(hi[0], hi[1]);
-        dst[w1] = __halves2half2(hi[2], hi[3]);
-        dst[32 + w0] = __halves2half2(lo[0], lo[1]);     // next column (lo): 8 uint4 = 32 half2 further
-        dst[32 + w1] = __halves2half2(lo[2], lo[3]);
+        const int w0 = (tt0 * 2 + blk) * 4 + jj * 2 + up;
+        dst[w0] = h01;
+        dst[w0 + 8] = h23;                                // thread tt0 + 1 of the fragment
+        dst[32 + w0] = l01;                               // next column (lo): 8 uint4 = 32 half2 further
+        dst[32 + w0 + 8] = l23;
     }
-    if (SUBN) {
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {                  // 8 consecutive lanes cover one 32-block of one row
-            shi += __shfl_xor_sync(0xFFFFFFFFu, shi, o);
-            slo += __shfl_xor_sync(0xFFFFFFFFu, slo, o);
-        }
-        if (on && (lane & 7) == 0) {
-            const float k8 = -8.f * 5.9604644775390625e-8f;     // -8 * 2^-24
-            float ch = k8 * shi, cl = k8 * slo;
-            cs[((size_t)chunk * M + m) * 2 + blk] = make_float4(ch, cl, 16.f * ch, 16.f * cl);
-        }
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);   // 8 consecutive lanes cover one 32-block of one row
+    if (on && (lane & 7) == 0) {
+        const float c = -8.f * 5.9604644775390625e-8f * sum;                        // -8 * 2^-24
+        reinterpret_cast<float2*>(cs + ((size_t)chunk * M + m))[blk] = make_float2(c, 16.f * c);
     }
 }
 
-// dynamic shared memory: ring [8 warps][depth][G units] | xs | cs | mbarriers
-// NX = float4 of x each thread keeps in registers between the max pass and the conversion pass
-//      (0: re-read x from global memory instead, for activations too long for the register file).
-template <bool SUBN, int G, int NX, int MINB>
-__global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4StreamLaunch p)
+// One pass over this thread's share of x (float4 index i = m * pk4 + f over M rows of pk4 float4): returns the largest
+// |x| bit pattern seen and, if CONVERT, stages the fragments with scale sc.
+template <bool CONVERT>
+__device__ __forceinline__ uint32_t q4s_stage_pass(const Q4StreamLaunch& p, int pk4, int total4, float sc, int ncols, uint4* xs,
+                                                   float4* cs, int tid, int lane, int threads)
+{
+    uint32_t mx = 0;
+    const int iters = (total4 + threads - 1) / threads;
+    for (int it0 = 0; it0 < iters; it0 += 4) {
+        float4 v[4];
+        int mm[4], ff[4];
+        bool on[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {                      // up to four loads in flight per thread
+            const int i = (it0 + u) * threads + tid;
+            on[u] = it0 + u < iters && i < total4;
+            const int ii = on[u] ? i : 0;
+            mm[u] = (ii >= pk4) + (ii >= 2 * pk4) + (ii >= 3 * pk4);       // M <= 4
+            ff[u] = ii - mm[u] * pk4;
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (on[u] && 4 * ff[u] < p.K) v[u] = *reinterpret_cast<const float4*>(p.X + (size_t)mm[u] * p.K + 4 * ff[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if ((it0 + u) * threads >= total4) break;       // the same for the whole CTA: nothing left to stage
+            mx = max(mx, __float_as_uint(v[u].x) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(v[u].y) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(v[u].z) & 0x7FFFFFFFu);
+            mx = max(mx, __float_as_uint(v[u].w) & 0x7FFFFFFFu);
+            if (CONVERT) q4s_stage_one(v[u], on[u], mm[u], ff[u], sc, ncols, p.M, xs, cs, lane);
+        }
+    }
+    return mx;
+}
+
+// dynamic shared memory: ring [16 warps][depth][G units] | xs | cs | mbarriers; after the runs are drained the start of
+// the ring is reused for the warps' parked partial tiles.
+// (NW, MINB) = (12 warps, 2 CTAs per SM) when the shared memory of a launch fits twice on an SM -- the next launch's
+// CTA is then resident beside this one's -- and (16, 1) for activations too long for that.
+template <int G, int NW, int MINB>
+__global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4StreamLaunch p)
 {
     constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
+    constexpr int THREADS = NW * 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ uint32_t s_max[Q4S_WARPS];
-    __shared__ float wpart[Q4S_WARPS][2][4][32];   // each warp's partial first / last tile, [q][lane]
-    __shared__ int wrp[Q4S_WARPS][2];              // the tile index of each, -1 if none
+    __shared__ uint32_t s_max[NW];
+    __shared__ int wrp[NW][2];                    // the tile index of each warp's parked partial tiles, -1 if none
     __shared__ uint4 zero_pg[2];                  // what lanes outside the 2M real columns read
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int M = p.M, ncols = 2 * M, nblk = p.nchunks * 2, D = p.depth;
+    const int M = p.M, ncols = 2 * M, D = p.depth;
+    Q4S_TRACE(0)
     if (lane < 2) wrp[warp][lane] = -1;
     if (tid < 2) zero_pg[tid] = make_uint4(0, 0, 0, 0);
     unsigned char* ring = smem_raw + (size_t)warp * D * STAGE_BYTES;
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)Q4S_WARPS * D * STAGE_BYTES);
-    float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)nblk * ncols * 64);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)nblk * M * 16) + warp * 8;
+    float* wpart = reinterpret_cast<float*>(smem_raw);        // [NW][2][4][32], valid after the runs are drained
+    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)NW * D * STAGE_BYTES);
+    float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)p.nchunks * ncols * 128);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)p.nchunks * M * 16) + warp * Q4S_MAX_DEPTH;
 
     const int W = p.warps_total;
-    const int gw = blockIdx.x * Q4S_WARPS + warp;
+    const int gw = blockIdx.x * NW + warp;
     const int gpr = p.nchunks / G;                            // groups per row pair-tile
     int cta_gb, cta_ge, gb, ge;
     if (p.tile_mode) {
         cta_gb = q4s_run_start((int)blockIdx.x, p.nrp, (int)gridDim.x) * gpr;
         cta_ge = q4s_run_start((int)blockIdx.x + 1, p.nrp, (int)gridDim.x) * gpr;
-        gb = cta_gb + q4s_run_start(warp, cta_ge - cta_gb, Q4S_WARPS);
-        ge = cta_gb + q4s_run_start(warp + 1, cta_ge - cta_gb, Q4S_WARPS);
+        gb = cta_gb + q4s_run_start(warp, cta_ge - cta_gb, NW);
+        ge = cta_gb + q4s_run_start(warp + 1, cta_ge - cta_gb, NW);
     } else {
-        cta_gb = q4s_run_start(min(W, (int)blockIdx.x * Q4S_WARPS), p.groups, W);
-        cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * Q4S_WARPS), p.groups, W);
+        cta_gb = q4s_run_start(min(W, (int)blockIdx.x * NW), p.groups, W);
+        cta_ge = q4s_run_start(min(W, (int)(blockIdx.x + 1) * NW), p.groups, W);
         gb = gw < W ? q4s_run_start(gw, p.groups, W) : 0;
         ge = gw < W ? q4s_run_start(gw + 1, p.groups, W) : 0;
     }
     const int ngroups = ge - gb;
     const unsigned char* gnext = reinterpret_cast<const unsigned char*>(p.stream) + (size_t)gb * STAGE_BYTES;
     const uint32_t ring_u32 = smem_u32(ring), bars_u32 = smem_u32(bars);
+    Q4S_TRACE(1)
 
     if (lane == 0) {
         for (int s = 0; s < D; ++s) mbar_init(&bars[s], 1);
@@ -729,8 +794,8 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
     __syncwarp();
     int issued = 0;
     const uint64_t l2pol = l2_evict_first_policy();
-    // Copies issued here are in flight when the dependency resolves, and the activation loads queue behind them:
-    // only p.pre stages go out now, the rest of the ring right after the activation loads have been issued.
+    // p.pre stages go out before the dependency on the previous kernel resolves, the rest of the ring right after the
+    // activation loads have been issued.
     auto issue_upto = [&](int n) {
         if (lane == 0) {
             for (; issued < n; ++issued) {
@@ -741,133 +806,100 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         }
     };
     issue_upto(min(min(D, p.pre), ngroups));
+    Q4S_TRACE(2)
 
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    Q4S_TRACE(3)
 
-    // ---- stage all of x as normalised hi/lo fp16 B fragments (same scheme as q4_linear_kernel)
+    // ---- stage all of x as hi/lo fp16 B fragments, scaled by the power of two that puts the largest |x| of the
+    // call in [2^14, 2^15): rows up to 2^17 times smaller than the largest keep full precision in the split.  A single
+    // row is first staged unscaled, in the same pass that finds its maximum, and that is kept when the maximum lies in
+    // [1, 2^15) (the split is then good to 2^-25 of it); otherwise, and for several rows, a second pass stages with the scale.
     const int pk4 = p.nchunks * 16;                       // float4 per activation row, padding included
     const int total4 = M * pk4;
-    float4 xv[NX > 0 ? NX : 1];
-    uint32_t mx = 0;
-    if (NX > 0) {
-#pragma unroll
-        for (int it = 0; it < NX; ++it) {
-            int i = it * Q4S_THREADS + tid;
-            int m = i / pk4, f = i - m * pk4;
-            xv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (i < total4 && 4 * f < p.K) xv[it] = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
-        }
-        issue_upto(min(D, ngroups));
-#pragma unroll
-        for (int it = 0; it < NX; ++it) {
-            mx = max(mx, __float_as_uint(xv[it].x) & 0x7FFFFFFFu);
-            mx = max(mx, __float_as_uint(xv[it].y) & 0x7FFFFFFFu);
-            mx = max(mx, __float_as_uint(xv[it].z) & 0x7FFFFFFFu);
-            mx = max(mx, __float_as_uint(xv[it].w) & 0x7FFFFFFFu);
-        }
-    } else {
-        issue_upto(min(D, ngroups));
-        for (int i = tid; i < total4; i += Q4S_THREADS) {
-            int m = i / pk4, f = i - m * pk4;
-            if (4 * f < p.K) {
-                float4 v = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
-                mx = max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu);
-                mx = max(mx, __float_as_uint(v.y) & 0x7FFFFFFFu);
-                mx = max(mx, __float_as_uint(v.z) & 0x7FFFFFFFu);
-                mx = max(mx, __float_as_uint(v.w) & 0x7FFFFFFFu);
-            }
-        }
-    }
+    uint32_t mx = M == 1 ? q4s_stage_pass<true>(p, pk4, total4, 1.f, ncols, xs, cs, tid, lane, THREADS)
+                         : q4s_stage_pass<false>(p, pk4, total4, 1.f, ncols, xs, cs, tid, lane, THREADS);
+    issue_upto(min(D, ngroups));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
     if (lane == 0) s_max[warp] = mx;
     __syncthreads();
     mx = s_max[0];
 #pragma unroll
-    for (int w = 1; w < Q4S_WARPS; ++w) mx = max(mx, s_max[w]);
-    int emax = (int)(mx >> 23);
-    float sc = 1.f, inv_sc = 1.f;
-    if (mx != 0 && emax < 255) {
-        emax = max(emax, 16);
-        sc = __uint_as_float((uint32_t)(268 - emax) << 23);
-        inv_sc = __uint_as_float((uint32_t)(emax - 14) << 23);
-    }
-    if (NX > 0) {
-#pragma unroll
-        for (int it = 0; it < NX; ++it) {
-            if (it * Q4S_THREADS >= total4) break;             // the same for the whole CTA: nothing left to stage
-            int i = it * Q4S_THREADS + tid;
-            bool on = i < total4;
-            int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
-            q4s_stage_one<SUBN>(xv[it], on, m, f, sc, M, ncols, xs, cs, lane);
+    for (int w = 1; w < NW; ++w) mx = max(mx, s_max[w]);
+    float inv_sc = 1.f;
+    if (M > 1 || (mx != 0 && (mx < 0x3F800000u || mx >= 0x47000000u))) {      // 1.0, 2^15
+        int emax = (int)(mx >> 23);
+        float sc = 1.f;
+        if (mx != 0 && emax < 255) {
+            emax = max(emax, 16);
+            sc = __uint_as_float((uint32_t)(268 - emax) << 23);
+            inv_sc = __uint_as_float((uint32_t)(emax - 14) << 23);
         }
-    } else {
-        const int iters = (total4 + Q4S_THREADS - 1) / Q4S_THREADS;
-        for (int it = 0; it < iters; ++it) {
-            int i = it * Q4S_THREADS + tid;
-            bool on = i < total4;
-            int m = on ? i / pk4 : 0, f = on ? i - m * pk4 : 0;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (on && 4 * f < p.K) v = *reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + 4 * f);
-            q4s_stage_one<SUBN>(v, on, m, f, sc, M, ncols, xs, cs, lane);
-        }
+        q4s_stage_pass<true>(p, pk4, total4, sc, ncols, xs, cs, tid, lane, THREADS);
+        __syncthreads();
     }
-    __syncthreads();
+    Q4S_TRACE(4)
 
     // ---- stream this warp's run
-    const float fA = (SUBN ? 16777216.f : 1.f) * inv_sc;     // 2^24: undo the subnormal weight encoding
-    const float fB = (SUBN ? 1048576.f : 1.f) * inv_sc;      // 2^20: rows g+8 carry an extra factor 16
+    const float fA = 16777216.f * inv_sc;                     // 2^24: undo the subnormal weight encoding
+    const float fB = 1048576.f * inv_sc;                      // 2^20: rows g+8 carry an extra factor 16
     float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     int rp = gb / gpr;
     int cg = gb - rp * gpr;                                   // group index inside the tile
     const int first_rp = rp;
-    // per-lane pointers into the staged activation; lanes outside the real columns sit on a page of zeros
-    const bool bvalid = g < ncols, cvalid = SUBN && t < M;
-    const uint4* xs0 = bvalid ? xs + (g * 4 + t) * 2 : zero_pg;
-    const float4* cs0 = cvalid ? cs + t * 2 : reinterpret_cast<const float4*>(zero_pg);
-    const int xstep = bvalid ? ncols * 8 : 0;                 // uint4 per chunk
-    const int cstep = cvalid ? M * 2 : 0;                     // float4 per chunk
-    const uint4* xsp = xs0 + (size_t)cg * G * xstep;
-    const float4* csp = cs0 + (size_t)cg * G * cstep;
+    // per-lane shared-memory addresses into the staged activation; lanes outside the real columns sit on a page of zeros
+    const bool bvalid = g < ncols, cvalid = t < M;
+    const uint32_t zero_u32 = smem_u32(zero_pg);
+    const uint32_t xs0 = bvalid ? smem_u32(xs) + (g * 4 + t) * 32 : zero_u32;
+    const uint32_t cs0 = cvalid ? smem_u32(cs) + t * 16 : zero_u32;
+    const uint32_t xstep = bvalid ? ncols * 128 : 0;          // bytes per chunk
+    const uint32_t cstep = cvalid ? M * 16 : 0;
+    uint32_t xsp = xs0 + cg * G * xstep;
+    uint32_t csp = cs0 + cg * G * cstep;
+    const uint32_t wlane = ring_u32 + lane * 16, slane = ring_u32 + 1024 + g * 16;
     int s = 0;
     uint32_t parity = 0;
 
-    // a tile wholly inside this warp's run goes straight to y; a tile it shares is parked in shared memory
+    // A tile wholly inside this warp's run goes straight to y.  A tile it shares with other warps (at most its first
+    // and its last one) is kept in registers until the whole CTA has drained its runs, then parked in shared memory.
+    float park[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    int park_rp[2] = {-1, -1};
     auto flush = [&](int tile_rp) {
         float v[4] = {acc[0][0] * fA, acc[0][1] * fB, acc[1][0] * fA, acc[1][1] * fB};
         const int r0 = tile_rp * gpr;
         if (gb <= r0 && r0 + gpr <= ge) {
             q4s_store_tile(p, v, tile_rp, lane);
+        } else if (tile_rp == first_rp) {
+            park[0][0] = v[0]; park[0][1] = v[1]; park[0][2] = v[2]; park[0][3] = v[3];
+            park_rp[0] = tile_rp;
         } else {
-            const int slot = tile_rp == first_rp ? 0 : 1;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) wpart[warp][slot][q][lane] = v[q];
-            if (lane == 0) wrp[warp][slot] = tile_rp;
+            park[1][0] = v[0]; park[1][1] = v[1]; park[1][2] = v[2]; park[1][3] = v[3];
+            park_rp[1] = tile_rp;
         }
     };
     bool timed_out = false;
 
     for (int j = 0; j < ngroups; ++j) {
         if (!mbar_wait(bars_u32 + s * 8, parity, Q4S_SPIN_LIMIT)) {
-            // record it, give the other copies in flight a short bounded chance to land, and leave
+            // Record it, issue nothing more, and give every copy still in flight the same generous bounded wait, so
+            // that none lands in shared memory after this CTA has left (if one still does not arrive, the hazard stays).
             if (lane == 0) {
                 atomicExch(p.status, 1);
-                for (int o = 1; o < D; ++o) {
-                    int s2 = (s + o) % D;
-                    mbar_wait(bars_u32 + s2 * 8, s2 > s ? parity : parity ^ 1u, 1u << 12);
-                }
+                for (int idx = j + 1; idx < issued; ++idx) mbar_wait(bars_u32 + (idx % D) * 8, (uint32_t)(idx / D) & 1u, Q4S_SPIN_LIMIT);
             }
             timed_out = true;
             break;
         }
-        const uint4* st = reinterpret_cast<const uint4*>(ring + (size_t)s * STAGE_BYTES);
+        const uint32_t st = s * STAGE_BYTES;
 #pragma unroll
         for (int q = 0; q < G; ++q) {
-            const uint4* un = st + q * Q4_UNIT_U4;
-            const uint4 w0 = un[lane], w1 = un[32 + lane], sv = un[64 + g];
-            const uint4 bf[2] = {xsp[0], xsp[1]};
-            const float4 cf[2] = {csp[0], csp[1]};
+            const uint4 w0 = lds128(wlane + st + q * Q4_UNIT_BYTES), w1 = lds128(wlane + st + q * Q4_UNIT_BYTES + 512);
+            const uint4 sv = lds128(slane + st + q * Q4_UNIT_BYTES);
+            const uint4 bf[2] = {lds128(xsp), lds128(xsp + 16)};
+            const uint4 cfu = lds128(csp);
+            const float4 cf = make_float4(__uint_as_float(cfu.x), __uint_as_float(cfu.y), __uint_as_float(cfu.z), __uint_as_float(cfu.w));
             xsp += xstep;
             csp += cstep;
             const uint32_t wt[2][4] = {{w0.x, w0.y, w0.z, w0.w}, {w1.x, w1.y, w1.z, w1.w}};
@@ -879,10 +911,10 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
 #pragma unroll
                 for (int b = 0; b < 2; ++b) {
                     uint32_t a0[4], a1[4];
-                    q4_unpack<SUBN>(wt[tile][2 * b], a0);
-                    q4_unpack<SUBN>(wt[tile][2 * b + 1], a1);
+                    q4_unpack<true>(wt[tile][2 * b], a0);
+                    q4_unpack<true>(wt[tile][2 * b + 1], a1);
                     float d[4];
-                    mma16816(d, a0, bf[b].x, bf[b].y, cf[b].x, cf[b].y, cf[b].z, cf[b].w);
+                    mma16816(d, a0, bf[b].x, bf[b].y, b ? cf.z : cf.x, 0.f, b ? cf.w : cf.y, 0.f);
                     mma16816(d, a1, bf[b].z, bf[b].w, d[0], d[1], d[2], d[3]);
                     acc[tile][0] = fmaf(b ? sA.y : sA.x, d[0] + d[1], acc[tile][0]);
                     acc[tile][1] = fmaf(b ? sB.y : sB.x, d[2] + d[3], acc[tile][1]);
@@ -908,12 +940,23 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         if (++s == D) { s = 0; parity ^= 1u; }
     }
     if (cg != 0 && !timed_out) flush(rp);  // the run ended inside a row pair-tile
+    Q4S_TRACE(5)
+    __syncthreads();                       // every warp has consumed every copy it issued: the ring is free
+    Q4S_TRACE(6)
+#pragma unroll
+    for (int slot = 0; slot < 2; ++slot) {
+        if (park_rp[slot] >= 0) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = park[slot][q];
+            if (lane == 0) wrp[warp][slot] = park_rp[slot];
+        }
+    }
     __syncthreads();
 
     // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
     // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
     const int cta_first_rp = cta_gb / gpr;
-    const int entry = wrp[lane >> 1][lane & 1];             // lane i holds segment i = (warp i/2, slot i%2)
+    const int entry = lane < 2 * NW ? wrp[lane >> 1][lane & 1] : -1;   // lane i holds segment i = (warp i/2, slot i%2)
 #pragma unroll
     for (int slot = 0; slot < 2; ++slot) {
         const int idx0 = warp * 2 + slot;
@@ -924,7 +967,7 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
         float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
         for (; same; same &= same - 1u) {                   // ascending segment order: a fixed summation order
             const int idx = __ffs(same) - 1;
-            const float* src = &wpart[idx >> 1][idx & 1][0][lane];
+            const float* src = wpart + (size_t)idx * 128 + lane;
             v0 += src[0]; v1 += src[32]; v2 += src[64]; v3 += src[96];
         }
         const int r0 = my * gpr, r1 = r0 + gpr;
@@ -932,16 +975,18 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const Q4Strea
             const float v[4] = {v0, v1, v2, v3};
             q4s_store_tile(p, v, my, lane);
         } else {
-            q4s_cross_cta(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
+            q4s_cross_cta<NW>(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
         }
     }
+
+    Q4S_TRACE(7)
 
     // ---- row-parallel: add the ranks' partial outputs.  The tagged pairs need no flag and no grid
     // barrier: an element is ready when all xworld copies of it carry the tag.
     if (p.xworld > 0) {
         const uint2* mine = p.xpeer[p.xrank];
         const int total = p.M * p.N;
-        for (int e = blockIdx.x * Q4S_THREADS + tid; e < total; e += gridDim.x * Q4S_THREADS) {
+        for (int e = blockIdx.x * THREADS + tid; e < total; e += gridDim.x * THREADS) {
             float sum = 0.f;
             bool ok = true;
             for (int r = 0; r < p.xworld && ok; ++r) {

@@ -88,8 +88,8 @@ class DecodeStack:
         self.stream = torch.cuda.Stream(device=self.dev)
         self.graph = None
         self.bytes_per_step = layers * sum(q4_bytes(N, K, M) for (_, N, K) in shapes)
-        self.launches_per_step = layers * len(shapes) * ((M + 15) // 16)
-        self.kernel_name = "q4_stream_kernel" if M <= 4 else "q4_linear_kernel"
+        self.launches_per_step = None          # counted by the library while the step is enqueued (capture())
+        self.kernel_name = "q4_stream_kernel" if M <= 4 else "q4_stream_kernel (slabs of <= 4 rows) / q4_linear_kernel"
 
     def _enqueue(self):
         import torch
@@ -105,7 +105,9 @@ class DecodeStack:
         import torch
         with torch.cuda.stream(self.stream):
             self._enqueue()
+            before = self.ctx.launches
             self._enqueue()
+            self.launches_per_step = self.ctx.launches - before
         self.stream.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, stream=self.stream):

@@ -84,6 +84,10 @@ class _Weight:
                                                           C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return out
 
+    def save(self, path: str):
+        """Write the weight as it lies in device memory (a cache file: see load_weight)."""
+        self.ctx.check(self.ctx.lib.mpq_weight_save(self.ctx.h, self.h, str(path).encode()))
+
     def destroy(self):
         if self.h:
             self.ctx.lib.mpq_weight_destroy(self.h)
@@ -94,6 +98,47 @@ class _Weight:
             self.destroy()
         except Exception:
             pass
+
+
+def load_weight(ctx: Context, path: str) -> "_Weight":
+    """Load a device-layout file written by ``_Weight.save``: no repack pass.  Raises MpqError with status
+    ERR_FORMAT when the file was written for another layout (or is damaged): rebuild from the canonical arrays."""
+    h = C.c_void_p()
+    ctx.check(ctx.lib.mpq_weight_load(ctx.h, str(path).encode(), C.byref(h)))
+    w = _Weight(ctx, h)
+    if w.fmt == _lib.FMT_NVFP4:
+        info = _lib.FileInfo()
+        ctx.check(ctx.lib.mpq_file_info(str(path).encode(), C.byref(info)))
+        w.tensor_scale = float(info.tensor_scale)
+    return w
+
+
+def save_canonical(path: str, fmt: int, codes: np.ndarray, scales: np.ndarray, tensor_scale: float = 1.0):
+    """Write the interchange arrays of a weight (no GPU needed)."""
+    lib = _lib.load()
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint16 if fmt == _lib.FMT_Q4 else np.uint8)
+    st = lib.mpq_canonical_save(str(path).encode(), fmt, codes.shape[0], codes.shape[1] * 2, _np_ptr(codes), _np_ptr(scales), C.c_float(tensor_scale))
+    if st != _lib.OK:
+        raise MpqError(st, lib.mpq_status_string(st).decode())
+
+
+def load_canonical(path: str):
+    """-> (fmt, codes, scales, tensor_scale) of a canonical file (no GPU needed)."""
+    lib = _lib.load()
+    info = _lib.FileInfo()
+    st = lib.mpq_file_info(str(path).encode(), C.byref(info))
+    if st == _lib.OK and info.kind != _lib.FILE_CANONICAL:
+        st = _lib.ERR_FORMAT
+    if st != _lib.OK:
+        raise MpqError(st, lib.mpq_status_string(st).decode())
+    codes = np.empty((info.N, info.K // 2), dtype=np.uint8)
+    scales = np.empty((info.N, info.K // 32), dtype=np.uint16) if info.fmt == _lib.FMT_Q4 else np.empty((info.N, info.K // 16), dtype=np.uint8)
+    ts = C.c_float()
+    st = lib.mpq_canonical_load(str(path).encode(), _np_ptr(codes), codes.nbytes, _np_ptr(scales), scales.nbytes, C.byref(ts))
+    if st != _lib.OK:
+        raise MpqError(st, lib.mpq_status_string(st).decode())
+    return info.fmt, codes, scales, float(ts.value)
 
 
 class Q4Weight(_Weight):

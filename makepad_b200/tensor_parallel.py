@@ -141,7 +141,7 @@ class TpDecodeStack:
     LAYOUT_70B_FFN = (("gate_up", 57344, 8192, _lib.TP_COLUMN), ("down", 8192, 28672, _lib.TP_ROW))
 
     def __init__(self, ctx: Context, rank: int, world: int, layers: int = 32, M: int = 1, seed: int = 0, fused: bool = True,
-                 layout=None):
+                 layout=None, keep_layer0: bool = False):
         import torch
         self.ctx, self.rank, self.world, self.layers, self.M, self.fused = ctx, rank, world, layers, M, fused
         if layout is not None:
@@ -155,7 +155,8 @@ class TpDecodeStack:
                 n, k = (N // world, K) if mode == _lib.TP_COLUMN else (N, K // world)
                 if mode == _lib.TP_ROW and (K // world) % 32:
                     raise ValueError(f"K={K} does not split into {world} multiples of 32")
-                self.weights.append(random_q4_weight_on_device(ctx, n, k, seed + 1000 * rank + layer * len(self.LAYOUT) + j))
+                self.weights.append(random_q4_weight_on_device(ctx, n, k, seed + 1000 * rank + layer * len(self.LAYOUT) + j,
+                                                               keep_canonical=keep_layer0 and layer == 0))
                 self.modes.append(mode)
         self.x_off, self.y_off, xo, yo = [], [], 0, 0
         for w in self.weights:
@@ -175,6 +176,7 @@ class TpDecodeStack:
         self.bytes_per_step = layers * sum(q4_bytes(N, K, M) for (_, N, K, _) in self.LAYOUT)     # whole job
         self.launches_per_step = layers * len(self.LAYOUT)
         self.kernel_name = "q4_stream_kernel"
+        self.use_fused = fused and M <= 4       # the in-kernel sum over ranks covers M <= 4; wider batches reduce with NCCL
 
     def _enqueue(self):
         import torch
@@ -185,7 +187,7 @@ class TpDecodeStack:
             xp = C.c_void_p(self.x.data_ptr() + 4 * self.x_off[i])
             yp = C.c_void_p(self.y.data_ptr() + 4 * self.y_off[i])
             if self.modes[i] == _lib.TP_ROW and self.world > 1:
-                if self.fused:
+                if self.use_fused:
                     ctx.check(lib.mpq_q4_linear_forward_allreduce(ctx.h, w.h, self.ex.h, xp, self.M, yp, s))
                 else:
                     ctx.check(lib.mpq_q4_linear_forward(ctx.h, w.h, xp, self.M, yp, s))
@@ -198,7 +200,9 @@ class TpDecodeStack:
         import torch.distributed as dist
         with torch.cuda.stream(self.stream):
             self._enqueue()
+            before = self.ctx.launches
             self._enqueue()
+            self.launches_per_step = self.ctx.launches - before
         self.stream.synchronize()
         if self.world > 1:
             dist.barrier()
@@ -209,6 +213,48 @@ class TpDecodeStack:
 
     def step(self):
         self.graph.replay()
+
+    def parity_of_layer0(self, orc, nrows: int = 256):
+        """Outputs of the first layer (after a step) against the CPU checker, on `nrows` sampled output rows per
+        projection.  Column-parallel projections: each rank checks its own slice.  Row-parallel ones: the ranks'
+        canonical shards and activations are gathered on rank 0, which checks the summed output and that every
+        rank holds the same bits.  Returns {"max_floored", "max_strict", "ok"} on rank 0, None elsewhere; needs
+        keep_layer0=True.  Not part of any timed region."""
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        worst_fl, worst_st, same = 0.0, 0.0, True
+        for i in range(len(self.LAYOUT)):
+            w = self.weights[i]
+            x = self.x[self.x_off[i]:self.x_off[i] + self.M * w.K].view(self.M, w.K).cpu().numpy()
+            y = self.y[self.y_off[i]:self.y_off[i] + self.M * w.N].view(self.M, w.N)
+            rows = np.unique(np.random.default_rng(i).choice(w.N, min(nrows, w.N), replace=False))
+            got = y[:, torch.from_numpy(rows).to(y.device)].cpu().numpy()
+            if self.modes[i] == _lib.TP_COLUMN or self.world == 1:
+                ref = orc.q4_matmul_f64(w.codes_host[rows], w.scales_host[rows], x)
+                st, fl = orc.rel_err(got, ref)
+                local = (st, fl, True)
+            else:
+                parts = [None] * self.world
+                dist.all_gather_object(parts, (w.codes_host[rows], w.scales_host[rows], x, got))
+                if self.rank == 0:
+                    ref = sum(orc.q4_matmul_f64(c, s_, x_) for (c, s_, x_, _) in parts)
+                    st, fl = orc.rel_err(got, ref)
+                    local = (st, fl, all(np.array_equal(parts[0][3], g) for (_, _, _, g) in parts))
+                else:
+                    local = (0.0, 0.0, True)
+            allv = [None] * self.world
+            if self.world > 1:
+                dist.all_gather_object(allv, local)
+            else:
+                allv = [local]
+            worst_st = max([worst_st] + [a[0] for a in allv])
+            worst_fl = max([worst_fl] + [a[1] for a in allv])
+            same = same and all(a[2] for a in allv)
+        if self.rank != 0:
+            return None
+        return {"max_floored": worst_fl, "max_strict": worst_st, "ranks_hold_same_bits": same, "ok": bool(worst_fl < 1e-3 and same),
+                "checked": f"layer 0, {nrows} sampled output rows per projection, against the CPU checker (binary64)"}
 
     def step_host(self):
         import torch

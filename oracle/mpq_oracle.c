@@ -333,6 +333,28 @@ void orc_nvfp4_gemm(int64_t M, int64_t N, int64_t K, const uint8_t* a, const uin
 /* vectorised conversions for the tests                                */
 /* ------------------------------------------------------------------ */
 
+/* Activation quantisation to NVFP4 (the usual recipe, stated here because the snapshot holds none): per row and
+ * 16-element block, amax = max |x|; the block scale is e4m3(amax / (6 * tscale)) (round to nearest even, saturating,
+ * 6 = the largest e2m1 magnitude); every element becomes e2m1(x / (e4m3_value * tscale)), round to nearest even,
+ * saturating; a block whose scale encodes to 0 gets all-zero codes.  All arithmetic in binary32. */
+void orc_nvfp4_quantize(int64_t R, int64_t K, const float* x, float tscale, uint8_t* codes, uint8_t* sf)
+{
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t b = 0; b < K / 16; ++b) {
+            const float* xb = x + r * K + 16 * b;
+            float amax = 0.0f;
+            for (int i = 0; i < 16; ++i) { float a = fabsf(xb[i]); if (a > amax) amax = a; }
+            uint8_t s8 = orc_f32_to_e4m3(amax / (6.0f * tscale));
+            float d = orc_e4m3_to_f32(s8) * tscale;
+            sf[r * (K / 16) + b] = s8;
+            for (int i = 0; i < 16; i += 2) {
+                uint8_t lo = d > 0.0f ? orc_f32_to_e2m1(xb[i] / d) : 0;
+                uint8_t hi = d > 0.0f ? orc_f32_to_e2m1(xb[i + 1] / d) : 0;
+                codes[r * (K / 2) + 8 * b + i / 2] = (uint8_t)(lo | (hi << 4));
+            }
+        }
+}
+
 void orc_f16_to_f32_n(const uint16_t* in, float* out, int64_t n) { for (int64_t i = 0; i < n; ++i) out[i] = orc_f16_to_f32(in[i]); }
 void orc_f32_to_f16_n(const float* in, uint16_t* out, int64_t n) { for (int64_t i = 0; i < n; ++i) out[i] = orc_f32_to_f16(in[i]); }
 void orc_f32_to_bf16_n(const float* in, uint16_t* out, int64_t n) { for (int64_t i = 0; i < n; ++i) out[i] = orc_f32_to_bf16(in[i]); }

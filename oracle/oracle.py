@@ -19,11 +19,31 @@ _LIB_PATH = os.path.join(_HERE, "liborc.so")
 _lib = None
 
 
+def _host_signature() -> str:
+    """What the binary was built for: it is compiled with -march=native, so a copy built on another machine
+    (it travels with the tree) must not be reused on this one."""
+    import hashlib
+    import platform
+    try:
+        with open("/proc/cpuinfo") as f:
+            lines = [ln for ln in f if ln.startswith(("model name", "flags"))][:2]
+    except OSError:
+        lines = []
+    return hashlib.sha1((platform.machine() + "".join(lines)).encode()).hexdigest()
+
+
 def build(force: bool = False) -> str:
-    """Compile ``mpq_oracle.c`` into ``liborc.so`` beside it (gcc, a second or two)."""
-    src = os.path.join(_HERE, "mpq_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    """Compile ``mpq_oracle.c`` into ``liborc.so`` beside it (gcc, a second or two), on the machine that runs it."""
+    src, mark = os.path.join(_HERE, "mpq_oracle.c"), os.path.join(_HERE, "liborc.host")
+    sig = _host_signature()
+    try:
+        built_for = open(mark).read().strip()
+    except OSError:
+        built_for = ""
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src) or built_for != sig:
         subprocess.check_call(["make", "-C", _HERE, "-B", "liborc.so"], stdout=subprocess.DEVNULL)
+        with open(mark, "w") as f:
+            f.write(sig + "\n")
     return _LIB_PATH
 
 
@@ -34,8 +54,7 @@ def _p(a, t):
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(_LIB_PATH):
-            build()
+        build()
         _lib = C.CDLL(_LIB_PATH)
     return _lib
 
@@ -128,6 +147,17 @@ def nvfp4_dequantize(codes, sf, tscale=1.0):
     return out
 
 
+def nvfp4_quantize(x, tscale=1.0):
+    """fp32 [R][K] -> (codes u8 [R][K/2], sf u8 [R][K/16]); see orc_nvfp4_quantize."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    R, K = x.shape
+    assert K % 16 == 0
+    codes = np.empty((R, K // 2), dtype=np.uint8)
+    sf = np.empty((R, K // 16), dtype=np.uint8)
+    lib().orc_nvfp4_quantize(C.c_int64(R), C.c_int64(K), _p(x, C.c_float), C.c_float(tscale), _p(codes, C.c_uint8), _p(sf, C.c_uint8))
+    return codes, sf
+
+
 def nvfp4_gemm(a, sfa, ta, b, sfb, tb, threads=0):
     """Returns (C fp32 [M,N], C bf16 bits [M,N]); B is stored [N][K/2]."""
     M, K = a.shape[0], a.shape[1] * 2
@@ -162,3 +192,14 @@ def rel_err(got, ref64, floor=1e-2):
     fl = np.maximum(np.abs(ref), floor * rms)
     floored = np.where(fl > 0, d / np.where(fl > 0, fl, 1), np.where(d == 0, 0.0, np.inf))
     return (float(strict.max()) if d.size else 0.0, float(floored.max()) if d.size else 0.0)
+
+
+def err_report(got, ref64):
+    """Every error figure the parity tests quote, in one dict: the strict maximum, the floored maxima with the
+    floor at 1e-2 and at 1e-3 of the output rms, and the largest absolute error as a fraction of the rms."""
+    ref = np.asarray(ref64, dtype=np.float64)
+    strict, fl2 = rel_err(got, ref, floor=1e-2)
+    _, fl3 = rel_err(got, ref, floor=1e-3)
+    rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
+    d = float(np.abs(np.asarray(got, dtype=np.float64) - ref).max()) if ref.size else 0.0
+    return {"strict": strict, "floored_1e-2_rms": fl2, "floored_1e-3_rms": fl3, "max_abs_over_rms": d / rms if rms > 0 else 0.0}

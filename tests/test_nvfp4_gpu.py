@@ -192,3 +192,99 @@ def test_error_statuses(ctx):
     x = torch.zeros(256, device="cuda")
     assert lib.mpq_q4_linear_forward(ctx.h, h, x.data_ptr(), 1, x.data_ptr(), None) == _lib.ERR_INVALID_ARG
     assert lib.mpq_weight_destroy(h) == _lib.OK
+
+
+def test_output_guard_regions_untouched(ctx):
+    """TMA tile stores clip at the tensor's edge: nothing is written outside C, for M and N off the tile grid."""
+    import torch
+    import makepad_b200
+    M, N, K = 130, 232, 288
+    a, sfa = synth.nvfp4_tensor(M, K, seed=21, stream=0)
+    b, sfb = synth.nvfp4_tensor(N, K, seed=21, stream=1)
+    w = makepad_b200.Nvfp4Weight(ctx, b, sfb, 1.0)
+    buf = torch.full((M * N + 4096,), 7.0, dtype=torch.bfloat16, device="cuda")
+    c = buf[2048:2048 + M * N].view(M, N)
+    for kernel in (None, "single"):
+        buf.fill_(7.0)
+        if kernel:
+            os.environ["MPQ_FP4_KERNEL"] = kernel
+        try:
+            makepad_b200.QuantLinear(w)((torch.from_numpy(a).cuda(), torch.from_numpy(sfa).cuda(), 1.0), out=c)
+            torch.cuda.synchronize()
+        finally:
+            os.environ.pop("MPQ_FP4_KERNEL", None)
+        assert (buf[:2048] == 7.0).all() and (buf[2048 + M * N:] == 7.0).all()
+    assert ctx.lib.mpq_context_poll_status(ctx.h) == _lib.OK
+    w.destroy()
+
+
+def test_error_metrics_strict_and_floored(ctx, orc):
+    """Strict and floored (1e-2 and 1e-3 of the rms) maxima of the bf16 output against the exact value: all three are
+    bounded by the bf16 rounding (2^-8), because the products are exact and the accumulation is fp32."""
+    a, sfa = synth.nvfp4_tensor(256, 1024, seed=5, stream=0)
+    b, sfb = synth.nvfp4_tensor(448, 1024, seed=5, stream=1)
+    c32, _ = orc.nvfp4_gemm(a, sfa, 1.0, b, sfb, 1.0)
+    got = orc.bf16_bits_to_f32(_gemm(ctx, a, sfa, 1.0, b, sfb, 1.0)).astype(np.float64)
+    rep = orc.err_report(got, c32.astype(np.float64))
+    print(f"NVFP4 256x448x1024: {rep}")
+    assert rep["floored_1e-2_rms"] < TOL and rep["floored_1e-3_rms"] < TOL
+
+
+def test_weight_export_reads_the_tiled_scales(ctx, orc):
+    """The weight keeps its scale factors only in the tiled order the GEMM consumes; the export un-tiles them, so a
+    bit-exact export proves the tiling pass (rows and K off the tile grid included)."""
+    import makepad_b200
+    for (N, K) in [(448, 512), (232, 288), (1000, 4096), (8, 32)]:
+        b, sfb = synth.nvfp4_tensor(N, K, seed=N + K)
+        w = makepad_b200.Nvfp4Weight(ctx, b, sfb, 0.5)
+        assert np.array_equal(w.dequantize().cpu().numpy().view(np.uint32), orc.nvfp4_dequantize(b, sfb, 0.5).view(np.uint32))
+        w.destroy()
+
+
+@pytest.mark.parametrize("M,K", [(1, 16), (7, 48), (200, 512), (2048, 4096)])
+def test_activation_quantisation_bit_exact(ctx, orc, M, K):
+    """fp32 and bf16 activations -> NVFP4 on the GPU: the same bytes as the CPU checker, and usable as the GEMM's A."""
+    import torch
+    rng = np.random.default_rng(M + K)
+    x = (rng.standard_normal((M, K)) * rng.uniform(1e-3, 50, size=(M, 1))).astype(np.float32)
+    x[0, :16] = 0                                                    # an all-zero block
+    if M > 1:
+        x[1, :4] = [448 * 6 * 2, -1e-9, 0.25, 0.75]                  # saturation, underflow, ties
+    for ts in (1.0, 0.37):
+        for bf16 in (0, 1):
+            xd = torch.from_numpy(x).cuda()
+            if bf16:
+                xd = xd.to(torch.bfloat16)
+                want_c, want_s = orc.nvfp4_quantize(xd.float().cpu().numpy(), ts)
+            else:
+                want_c, want_s = orc.nvfp4_quantize(x, ts)
+            codes = torch.empty((M, K // 2), dtype=torch.uint8, device="cuda")
+            sf = torch.empty((M, K // 16), dtype=torch.uint8, device="cuda")
+            ctx.check(ctx.lib.mpq_nvfp4_quantize_activations(ctx.h, C.c_void_p(xd.data_ptr()), bf16, M, K, C.c_float(ts),
+                                                             C.c_void_p(codes.data_ptr()), C.c_void_p(sf.data_ptr()), None))
+            torch.cuda.synchronize()
+            assert np.array_equal(sf.cpu().numpy(), want_s)
+            assert np.array_equal(codes.cpu().numpy(), want_c)
+    assert ctx.lib.mpq_nvfp4_quantize_activations(ctx.h, C.c_void_p(xd.data_ptr()), 0, M, 24, C.c_float(1.0), C.c_void_p(codes.data_ptr()),
+                                                  C.c_void_p(sf.data_ptr()), None) == _lib.ERR_SHAPE
+
+
+def test_quantise_then_gemm(ctx, orc):
+    """The prefill chain: quantise fp32 activations on the GPU, feed them to the GEMM; equal to the checker's chain."""
+    import torch
+    import makepad_b200
+    M, N, K = 256, 448, 1024
+    x = synth.activations(M, K, seed=17)
+    b, sfb = synth.nvfp4_tensor(N, K, seed=17, stream=1)
+    xd = torch.from_numpy(x).cuda()
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device="cuda")
+    sf = torch.empty((M, K // 16), dtype=torch.uint8, device="cuda")
+    ctx.check(ctx.lib.mpq_nvfp4_quantize_activations(ctx.h, C.c_void_p(xd.data_ptr()), 0, M, K, C.c_float(1.0), C.c_void_p(codes.data_ptr()),
+                                                     C.c_void_p(sf.data_ptr()), None))
+    w = makepad_b200.Nvfp4Weight(ctx, b, sfb, 1.0)
+    y = makepad_b200.QuantLinear(w)((codes, sf, 1.0))
+    torch.cuda.synchronize()
+    a_c, a_s = orc.nvfp4_quantize(x, 1.0)
+    c32, _ = orc.nvfp4_gemm(a_c, a_s, 1.0, b, sfb, 1.0)
+    _check(orc, y.view(torch.int16).cpu().numpy().view(np.uint16), c32)
+    w.destroy()

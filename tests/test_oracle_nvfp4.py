@@ -64,3 +64,30 @@ def test_golden_vectors(orc):
         assert np.array_equal(c32.view(np.uint32), g[f"fp4_{i}_c32"].view(np.uint32))
         assert np.array_equal(c16, g[f"fp4_{i}_c16"])
         assert np.array_equal(orc.nvfp4_dequantize(b, sfb, 1.0).view(np.uint32), g[f"fp4_{i}_deq_b"].view(np.uint32))
+
+
+def test_activation_quantisation_known_answers_and_bounds():
+    """orc_nvfp4_quantize: hand-checked blocks, and the error bound of the format on random data."""
+    from oracle import oracle as orc
+    orc.build()
+    x = np.zeros((1, 32), dtype=np.float32)
+    x[0, :16] = [6, -6, 3, 1.5, 0.5, 0.25, 0.26, -0.74, 0.75, 1.25, 1.26, 2.5, 2.6, 5.0, 5.1, 0]
+    codes, sf = orc.nvfp4_quantize(x, 1.0)
+    assert sf[0, 0] == 0x38 and sf[0, 1] == 0                      # amax 6 -> scale 1.0 (e4m3 0x38); the all-zero block -> 0
+    nib = np.stack([codes[0, :8] & 0xF, codes[0, :8] >> 4], axis=1).reshape(-1)
+    # ties go to the even mantissa: 0.25 -> 0, 0.75 -> 1.0, 1.25 -> 1.0, 2.5 -> 2, 5.0 -> 4
+    assert list(nib) == [7, 15, 5, 3, 1, 0, 1, 9, 2, 2, 3, 4, 5, 6, 7, 0]
+    assert not codes[0, 8:].any()
+    # scale rounding and saturation
+    x2 = np.full((1, 16), 448.0 * 6 * 4, dtype=np.float32)
+    c2, s2 = orc.nvfp4_quantize(x2, 1.0)
+    assert s2[0, 0] == 0x7E and (c2 == 0x77).all()                 # scale saturates at 448, codes at 6
+    rng = np.random.default_rng(3)
+    x3 = (rng.standard_normal((8, 256)) * rng.uniform(0.01, 100, size=(8, 1))).astype(np.float32)
+    for ts in (1.0, 0.37):
+        c3, s3 = orc.nvfp4_quantize(x3, ts)
+        back = orc.nvfp4_dequantize(c3, s3, ts)
+        amax = np.abs(x3.reshape(8, 16, 16)).max(axis=2, keepdims=True)
+        err = np.abs(back - x3).reshape(8, 16, 16)
+        # e2m1 steps are at most 2 (between 4 and 6) in units of amax/6 (scale rounding adds < 1/16): error <= ~amax/6 * 1.07
+        assert (err <= amax / 6 * 1.07 + 1e-12).all()

@@ -44,6 +44,90 @@ def test_world1_exchange_path_equals_plain_forward(ctx, orc):
     ex.destroy()
 
 
+def test_allreduce_output_guard_regions_untouched(ctx):
+    import torch
+    from makepad_b200.tensor_parallel import Exchange, RowParallelLinear
+    N, K, M = 1000, 2048, 3
+    codes, scales = synth.q4_weight(N, K, seed=23)
+    ex = Exchange(ctx, 0, 1, max_floats=M * N)
+    row = RowParallelLinear(ctx, codes, scales, 0, 1, exchange=ex)
+    buf = torch.full((M * N + 512,), 321.0, device="cuda")
+    y = buf[256:256 + M * N]
+    x = torch.from_numpy(synth.activations(M, K, seed=24)).cuda()
+    for _ in range(2):
+        ctx.check(ctx.lib.mpq_q4_linear_forward_allreduce(ctx.h, row.w.h, ex.h, x.data_ptr(), M, y.data_ptr(), None))
+    torch.cuda.synchronize()
+    assert (buf[:256] == 321.0).all() and (buf[256 + M * N:] == 321.0).all() and not (y == 321.0).any()
+    ex.destroy()
+
+
+def test_odd_number_of_captured_calls_is_reported(ctx):
+    """A replayed graph must hold an even number of calls on one exchange (they alternate between the halves of
+    the buffer); the library counts the calls of a stream capture and reports an odd count."""
+    import torch
+    from makepad_b200.tensor_parallel import Exchange, RowParallelLinear
+    lib = ctx.lib
+    codes, scales = synth.q4_weight(256, 512, seed=25)
+    ex = Exchange(ctx, 0, 1, max_floats=256)
+    row = RowParallelLinear(ctx, codes, scales, 0, 1, exchange=ex)
+    x = torch.from_numpy(synth.activations(1, 512, seed=26)).cuda()
+    y = torch.empty((1, 256), device="cuda")
+    side = torch.cuda.Stream()
+
+    def enqueue(n):
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for _ in range(n):
+            ctx.check(lib.mpq_q4_linear_forward_allreduce(ctx.h, row.w.h, ex.h, x.data_ptr(), 1, y.data_ptr(), s))
+
+    with torch.cuda.stream(side):
+        enqueue(2)                                       # eager calls are not counted
+    side.synchronize()
+    assert lib.mpq_exchange_graph_check(ex.h) == _lib.OK
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        enqueue(3)
+    assert lib.mpq_exchange_graph_check(ex.h) == _lib.ERR_STATE      # odd: reported, and cleared by the check
+    assert lib.mpq_exchange_graph_check(ex.h) == _lib.OK
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2, stream=side):
+        enqueue(1)
+    # without the check, the next forward call reports it
+    with torch.cuda.stream(side):
+        st = lib.mpq_q4_linear_forward_allreduce(ctx.h, row.w.h, ex.h, x.data_ptr(), 1, y.data_ptr(), C.c_void_p(side.cuda_stream))
+    assert st == _lib.ERR_STATE and b"odd number" in lib.mpq_last_error(ctx.h)
+    assert lib.mpq_exchange_graph_check(ex.h) == _lib.ERR_STATE
+    g3 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g3, stream=side):
+        enqueue(4)
+    assert lib.mpq_exchange_graph_check(ex.h) == _lib.OK
+    g3.replay(); g3.replay()
+    torch.cuda.synchronize()
+    assert lib.mpq_context_poll_status(ctx.h) == _lib.OK
+    del g, g2, g3
+    ex.destroy()
+
+
+def test_two_contexts_in_one_process_on_two_devices(orc):
+    """Kernel attributes are per device: a second context on another GPU of the same process must work too."""
+    import torch
+    import makepad_b200
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    codes, scales = synth.q4_weight(512, 4096, seed=27)
+    x = synth.activations(2, 4096, seed=28)
+    ref = orc.q4_matmul_f64(codes, scales, x)
+    for dev in (0, 1):
+        c = makepad_b200.Context(dev)
+        w = makepad_b200.Q4Weight(c, codes, scales)
+        with torch.cuda.device(dev):
+            xd = torch.from_numpy(x).to(f"cuda:{dev}")
+            y = makepad_b200.QuantLinear(w)(xd)
+            torch.cuda.synchronize(dev)
+        assert orc.rel_err(y.cpu().numpy(), ref)[1] < 1e-3
+        w.destroy()
+        c.close()
+
+
 def test_exchange_call_order_and_arguments(ctx):
     lib = ctx.lib
     h = C.c_void_p()

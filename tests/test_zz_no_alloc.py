@@ -20,7 +20,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
     lib = ctx.lib
     s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    for (N, K) in [(4096, 4096), (1000, 2048), (4096, 11008)]:       # tiles shared between CTAs in all of them
+    # (1024, 11008) and (1000, 2112) have too few rows for whole tiles per CTA: their row tiles straddle the runs of
+    # several CTAs, whose partial sums meet in the static array (the other shapes never touch it)
+    for (N, K) in [(4096, 4096), (1024, 11008), (1000, 2112), (4096, 11008)]:
         codes, scales = synth.q4_weight(N, K, seed=31)
         w = makepad_b200.Q4Weight(ctx, codes, scales)
         for M in (1, 3, 4, 7, 20):                                   # M > 4 runs as several launches
@@ -47,4 +49,18 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
     assert lib.mpq_q4_linear_forward_static(ctx.h, w.h, C.c_void_p(x.data_ptr() + 4), 1, C.c_void_p(y.data_ptr()), None, s) == _lib.ERR_ALIGN
     assert lib.mpq_q4_linear_forward_static(ctx.h, w.h, None, 1, C.c_void_p(y.data_ptr()), None, s) == _lib.ERR_INVALID_ARG
     torch.cuda.synchronize()
+    # no allocation: with every buffer made beforehand, the device's free memory is the same after a series of calls
+    codes, scales = synth.q4_weight(1024, 11008, seed=34)
+    w2 = makepad_b200.Q4Weight(ctx, codes, scales)
+    x = torch.from_numpy(synth.activations(6, 11008, seed=35)).cuda()
+    y = torch.empty((6, 1024), device="cuda")
+    ctx.check(lib.mpq_q4_linear_forward_static(ctx.h, w2.h, C.c_void_p(x.data_ptr()), 6, C.c_void_p(y.data_ptr()), None, s))
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for M in (1, 2, 4, 6):
+        ctx.check(lib.mpq_q4_linear_forward_static(ctx.h, w2.h, C.c_void_p(x.data_ptr()), M, C.c_void_p(y.data_ptr()), None, s))
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    # with no status pointer, a timeout would be recorded in the array's own status word, which the context's poll reads
+    assert lib.mpq_context_poll_status(ctx.h) == _lib.OK
     ctx.close()
