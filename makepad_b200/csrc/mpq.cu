@@ -18,6 +18,7 @@
 #include "nvfp4.cuh"
 #include "per_device.h"
 #include "q4.cuh"
+#include "q4_rect.cuh"
 
 using namespace mpq;
 
@@ -34,6 +35,9 @@ struct mpq_context {
     size_t hx_bytes, hy_bytes;
     // scratch of the streaming Q4 kernel: tagged partial tiles of row pair-tiles cut by a boundary
     // between two CTAs' runs (two slots per CTA; write-once / read-once per launch), one status word
+    float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
+    size_t q4_rect_partial_bytes;
+    bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
     uint2* q4_partials;
     int q4_partials_ctas;
     int* q4_status;
@@ -131,6 +135,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->hx = c->hy = nullptr;
     c->hx_bytes = c->hy_bytes = 0;
     c->q4_partials = nullptr;
+    c->q4_rect_partial = nullptr;
+    c->q4_rect_partial_bytes = 0;
     c->q4_partials_ctas = 0;
     c->q4_status = nullptr;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&c->prop, device) != cudaSuccess) {
@@ -157,6 +163,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_depth_full = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_PRE");
     c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : -1;
+    e = getenv("MPQ_Q4_RECT");
+    c->q4_rect = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_SLAB4");
     c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
@@ -172,6 +180,7 @@ extern "C" int32_t mpq_context_destroy(mpq_context* ctx)
     cudaFree(ctx->hx);
     cudaFree(ctx->hy);
     cudaFree(ctx->q4_partials);
+    cudaFree(ctx->q4_rect_partial);
     cudaFree(ctx->q4_status);
     ctx->fp4.release();
     ctx->magic = 0;
@@ -418,7 +427,9 @@ static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4Stre
     if (!ctx->q4_stream || M > 4) return false;
     // the ring with the most bytes that fits (ties: the larger copies), at least dmin stages deep
     auto fit = [&](int nw, size_t budget, int dmax, int dmin) {
-        const size_t fixed = (size_t)q.nchunks * 256 * M + (size_t)q.nchunks * 16 * M + (size_t)nw * Q4S_MAX_DEPTH * 8;
+        // activation fragments + corrections + barriers (+ the parked partial tiles, a region of their own in the one-CTA form)
+        const size_t fixed = (size_t)q.nchunks * 256 * M + (size_t)q.nchunks * 16 * M + (size_t)nw * Q4S_MAX_DEPTH * 8 +
+                             (nw == Q4S_WARPS_FULL ? (size_t)nw * 2 * 4 * 32 * 4 : 0);
         size_t best = 0;
         pl->nw = nw;
         for (int G = 2; G >= 1; --G) {
@@ -487,6 +498,7 @@ static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4Stre
     p->partials = nullptr; p->status = nullptr;
     p->xworld = 0; p->xrank = 0; p->xslot = 0; p->xlimit = 0;
     for (int r = 0; r < 8; ++r) p->xpeer[r] = nullptr;
+    p->xmine = nullptr;
     return p->tile_mode ? std::min(sms, q.nrp) : (W + pl.nw - 1) / pl.nw;
 }
 
@@ -505,8 +517,8 @@ static int32_t q4_stream_enqueue(mpq_context* ctx, const Q4StreamPlan& pl, const
 {
 #ifdef MPQ_TRACE
     Q4StreamLaunch p = p_in;
-    if (!g_trace && cudaMallocManaged(&g_trace, (size_t)64 * 1024 * 8 * 8) != cudaSuccess) g_trace = nullptr;
-    p.trace = (g_trace && grid <= 1024) ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 8 : nullptr;
+    if (!g_trace && cudaMallocManaged(&g_trace, (size_t)64 * 1024 * 16 * 8) != cudaSuccess) g_trace = nullptr;
+    p.trace = (g_trace && grid <= 1024) ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 16 : nullptr;
 #else
     const Q4StreamLaunch& p = p_in;
 #endif
@@ -532,8 +544,121 @@ static int32_t q4_stream_forward(mpq_context* ctx, const Q4Dev& q, const Q4Strea
         const size_t half = (size_t)(++ex->calls & 1u) * ex->world * ex->max_floats;
         p.xworld = ex->world; p.xrank = ex->rank; p.xslot = ex->max_floats; p.xlimit = ex->wait_limit;
         for (int r = 0; r < ex->world; ++r) p.xpeer[r] = ex->peer[r] + half;
+        p.xmine = p.xpeer[ex->rank];
     }
     return q4_stream_enqueue(ctx, pl, p, grid, s);
+}
+
+// ---------------------------------------------------------------------------
+// the rectangle kernel: up to 16 rows, any K, weights read once
+// ---------------------------------------------------------------------------
+struct Q4RectPlan { int mt, depth, slice_chunks, nks, ntg; size_t smem; };
+static bool q4_rect_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4RectPlan* pl)
+{
+    if (M < 1 || M > 16) return false;
+    const int mt = (M + 3) / 4, mp = 4 * mt;
+    const int sms = ctx->prop.multiProcessorCount;
+    const size_t per_chunk = (size_t)2 * mp * 128 + (size_t)2 * mp * 8;          // fragments + corrections
+    const size_t wpart = (size_t)Q4R_WARPS * 2 * (4 * mt) * 32 * 4, bars = (size_t)Q4R_WARPS * Q4S_MAX_DEPTH * 8;
+    const size_t total = (size_t)227 * 1024 - 512;
+    for (int depth = 2; depth >= 1; --depth) {
+        const size_t ring = (size_t)Q4R_WARPS * depth * Q4R_STAGE_BYTES;
+        if (ring + wpart + bars + per_chunk * Q4R_G > total) continue;
+        int max_slice = (int)((total - ring - wpart - bars) / per_chunk) / Q4R_G * Q4R_G;
+        // K slices: as few as fit, but enough of them that tile groups x slices can cover the SMs
+        int nks = (q.nchunks + max_slice - 1) / max_slice;
+        while (nks < 16 && (int64_t)q.nrp * nks < sms && q.nchunks / (nks + 1) >= 2 * Q4R_G) ++nks;
+        int slice = ((q.nchunks + nks - 1) / nks + Q4R_G - 1) / Q4R_G * Q4R_G;
+        nks = (q.nchunks + slice - 1) / slice;
+        pl->mt = mt; pl->depth = depth; pl->slice_chunks = slice; pl->nks = nks;
+        if (nks > sms) continue;                           // (cannot happen for K below a few million)
+        pl->ntg = std::max(1, std::min(q.nrp, sms / nks));
+        pl->smem = ring + per_chunk * slice + wpart + bars;
+        return true;
+    }
+    return false;
+}
+
+template <int MT>
+static cudaError_t q4_rect_launch_t(int device, const Q4RectLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
+{
+    auto kern = q4_rect_kernel<MT>;
+    static PerDeviceOnce configured;
+    if (configured.needs(device)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 512));
+        if (e != cudaSuccess) return e;
+        configured.mark(device);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(Q4R_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+}
+
+static int32_t q4_status_word(mpq_context* ctx)
+{
+    if (!ctx->q4_status) {
+        CU_TRY(ctx, cudaMalloc(&ctx->q4_status, sizeof(int)));
+        CU_TRY(ctx, cudaMemset(ctx->q4_status, 0, sizeof(int)));
+    }
+    return MPQ_OK;
+}
+
+// One slab of M <= 16 rows through the rectangle kernel (plus the slice-sum kernel when K was cut).
+static int32_t q4_rect_forward(mpq_context* ctx, const Q4Dev& q, const Q4RectPlan& pl, const float* x, int M, float* y, int64_t ldy,
+                               cudaStream_t s)
+{
+    int32_t st = q4_status_word(ctx);
+    if (st) return st;
+    if (pl.nks > 1) {
+        const size_t need = (size_t)pl.nks * M * q.N * sizeof(float);
+        if (ctx->q4_rect_partial_bytes < need) {
+            CU_TRY(ctx, cudaDeviceSynchronize());          // nobody may still be using the old array
+            cudaFree(ctx->q4_rect_partial);
+            ctx->q4_rect_partial = nullptr;
+            ctx->q4_rect_partial_bytes = 0;
+            CU_TRY(ctx, cudaMalloc(&ctx->q4_rect_partial, need));
+            ctx->q4_rect_partial_bytes = need;
+        }
+    }
+    Q4RectLaunch p;
+    p.stream = q.stream; p.X = x; p.Y = y; p.partial = ctx->q4_rect_partial;
+    p.M = M; p.N = (int)q.N; p.K = (int)q.K; p.ldy = ldy;
+    p.nchunks = q.nchunks; p.nrp = q.nrp; p.ntg = pl.ntg; p.nks = pl.nks; p.slice_chunks = pl.slice_chunks; p.depth = pl.depth;
+    p.status = ctx->q4_status;
+    const int grid = pl.ntg * pl.nks;
+    cudaError_t e;
+    switch (pl.mt) {
+        case 1: e = q4_rect_launch_t<1>(ctx->device, p, grid, pl.smem, ctx->pdl, s); break;
+        case 2: e = q4_rect_launch_t<2>(ctx->device, p, grid, pl.smem, ctx->pdl, s); break;
+        case 3: e = q4_rect_launch_t<3>(ctx->device, p, grid, pl.smem, ctx->pdl, s); break;
+        default: e = q4_rect_launch_t<4>(ctx->device, p, grid, pl.smem, ctx->pdl, s); break;
+    }
+    ctx->launches += 1;
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_rect_kernel launch failed: %s", cudaGetErrorString(e));
+    if (pl.nks > 1) {
+        cudaLaunchConfig_t cfg = {};
+        const int64_t total = (int64_t)M * q.N;
+        cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->prop.multiProcessorCount * 8));
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = ctx->pdl ? 1u : 0u;
+        e = cudaLaunchKernelEx(&cfg, q4_rect_reduce_kernel, (const float*)ctx->q4_rect_partial, pl.nks, M, (int)q.N, y, ldy);
+        ctx->launches += 1;
+        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_rect_reduce_kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return MPQ_OK;
 }
 
 // One launch for a slab of M <= 16 activation rows.
@@ -541,7 +666,9 @@ static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float*
 static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
 {
     Q4StreamPlan pl;
-    if (q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
+    if (M <= 4 && q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
+    Q4RectPlan rp;
+    if (ctx->q4_rect && q4_rect_plan(ctx, q, M, &rp)) return q4_rect_forward(ctx, q, rp, x, M, y, ldy, s);
     return q4_forward_general(ctx, q, x, M, y, ldy, s);
 }
 
@@ -575,12 +702,13 @@ static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float*
     return MPQ_OK;
 }
 
-// Rows per launch for M activation rows: the streaming kernel's widest slab (4, 2 or 1 rows) whose staged
-// activation fits in shared memory, else 16 through the phase-staged kernel.
+// Rows per launch for M activation rows: up to 4 through the streaming kernel when the activation fits in shared
+// memory, else up to 16 through the rectangle kernel (weights read once per slab of 16).
 static int q4_slab_rows(const mpq_context* ctx, const Q4Dev& q, int64_t M)
 {
     Q4StreamPlan pl;
     if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) return (int)M;      // one launch of the streaming kernel
+    if (ctx->q4_rect) return 16;
     if (ctx->q4_slab4 && M > 1) {
         const int widths[3] = {4, 2, 1};
         for (int i = 0; i < 3; ++i)
@@ -592,9 +720,6 @@ static int q4_slab_rows(const mpq_context* ctx, const Q4Dev& q, int64_t M)
 static int32_t q4_forward_checked(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M, float* y_dev,
                                   int64_t ldy, cudaStream_t s)
 {
-    // M > 4: slabs of four rows through the streaming kernel where it applies (it re-reads the weights per
-    // slab but runs near the HBM roofline), else slabs of sixteen through the phase-staged kernel, whose
-    // legacy-MMA arithmetic is the bound from M = 8 up.
     const int slab = q4_slab_rows(ctx, w->q4, M);
     for (int64_t m0 = 0; m0 < M; m0 += slab) {
         int m = (int)std::min<int64_t>(slab, M - m0);
@@ -683,7 +808,19 @@ extern "C" int32_t mpq_q4_linear_forward_static(mpq_context* ctx, const mpq_weig
     unsigned char* base = g_q4_static_ptr[ctx->device];
     const Q4Dev& q = w->q4;
     cudaStream_t s = (cudaStream_t)stream;
-    const int slab = q4_slab_rows(ctx, q, M);          // the same split into launches as mpq_q4_linear_forward
+    // Slabs of up to four rows through the streaming kernel (whose scratch is the static array); where the
+    // activation is too long for it, sixteen rows at a time through the phase-staged kernel, which needs no
+    // scratch.  (The rectangle kernel that mpq_q4_linear_forward uses above four rows may need a scratch
+    // array sized by the call, so it is not used here: above four rows the two entry points agree to
+    // rounding, not bit for bit.)
+    int slab = 16;
+    {
+        Q4StreamPlan pl;
+        const int widths[3] = {4, 2, 1};
+        for (int i = 2; i >= 0; --i)
+            if (widths[i] <= M && q4_stream_plan(ctx, q, widths[i], &pl)) slab = widths[i];
+        if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) slab = (int)M;
+    }
     for (int64_t m0 = 0; m0 < M; m0 += slab) {
         const int m = (int)std::min<int64_t>(slab, M - m0);
         const float* x = x_dev + (size_t)m0 * q.K;
@@ -1168,9 +1305,12 @@ __global__ void __launch_bounds__(512) hbm_read_probe_kernel(const uint4* __rest
     uint32_t acc = 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < n16; i += 4 * stride) {        // four loads in flight per thread
-        uint4 a = ldg_stream(src + i), b = ldg_stream(src + i + stride), c = ldg_stream(src + i + 2 * stride), d = ldg_stream(src + i + 3 * stride);
-        acc += (a.x ^ a.y ^ a.z ^ a.w) + (b.x ^ b.y ^ b.z ^ b.w) + (c.x ^ c.y ^ c.z ^ c.w) + (d.x ^ d.y ^ d.z ^ d.w);
+    for (; i + 7 * stride < n16; i += 8 * stride) {        // eight loads in flight per thread
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ldg_stream(src + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
     }
     for (; i < n16; i += stride) {
         uint4 a = ldg_stream(src + i);

@@ -484,10 +484,12 @@ struct Q4StreamLaunch {
     // halves of the buffer, so a fast rank cannot overwrite what a slow rank has not read yet.
     int xworld, xrank;
     uint2* xpeer[8];        // rank r's exchange buffer (this rank's own for r == xrank), already offset to this launch's half
+    uint2* xmine;           // == xpeer[xrank] (a separate field: the array is only ever indexed by constants, which
+                            // keeps the parameter block out of local memory)
     int64_t xslot;          // uint2 per slot (>= M * N)
     uint32_t xlimit;        // polls of one element before giving up
 #ifdef MPQ_TRACE
-    unsigned long long* trace;   // [CTAs][8] %globaltimer stamps of thread 0 (diagnostic build only)
+    unsigned long long* trace;   // [CTAs][16]: %globaltimer stamps of thread 0, then warp 0's cycle counts (diagnostic build only)
 #endif
 };
 
@@ -497,10 +499,14 @@ struct Q4StreamLaunch {
     if (p.trace && tid == 0) {                                                 \
         unsigned long long t_;                                                 \
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                 \
-        p.trace[(size_t)blockIdx.x * 8 + (slot)] = t_;                         \
+        p.trace[(size_t)blockIdx.x * 16 + (slot)] = t_;                        \
     }
+#define Q4S_CYC(var) long long var = clock64();
+#define Q4S_CYC_ADD(acc, since) acc += clock64() - (since);
 #else
 #define Q4S_TRACE(slot)
+#define Q4S_CYC(var)
+#define Q4S_CYC_ADD(acc, since)
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -611,7 +617,9 @@ __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const fl
             if (n < p.N) {
                 if (p.xworld > 0) {                      // plain peer stores over NVLink: one 8-byte store per rank
                     const size_t e = (size_t)p.xrank * p.xslot + (size_t)t * p.N + n;
-                    for (int r = 0; r < p.xworld; ++r) st_tagged_sys(p.xpeer[r] + e, v[q], 1u);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r)
+                        if (r < p.xworld) st_tagged_sys(p.xpeer[r] + e, v[q], 1u);
                 } else {
                     p.Y[(size_t)t * p.ldy + n] = v[q];
                 }
@@ -692,12 +700,15 @@ __device__ __forceinline__ void q4s_stage_one(float4 v, bool on, int m, int f, f
     const int chunk = f >> 4, r = f & 15;
     const int blk = r >> 3, jj = (r >> 2) & 1, up = (r >> 1) & 1, tt0 = (r & 1) * 2;
     if (on) {
+        // Column c keeps its eight 16-byte slots (t, block) at slot ^ (c & 7): the eight columns an MMA's lanes read
+        // together then fall into different banks.
         __half2* dst = reinterpret_cast<__half2*>(xs + ((size_t)chunk * ncols + 2 * m) * 8);   // 8 uint4 per column
-        const int w0 = (tt0 * 2 + blk) * 4 + jj * 2 + up;
-        dst[w0] = h01;
-        dst[w0 + 8] = h23;                                // thread tt0 + 1 of the fragment
-        dst[32 + w0] = l01;                               // next column (lo): 8 uint4 = 32 half2 further
-        dst[32 + w0 + 8] = l23;
+        const int s0 = tt0 * 2 + blk, s1 = s0 + 2, in = jj * 2 + up;                           // thread tt0 and tt0 + 1 of the fragment
+        const int chi = (2 * m) & 7, clo = (2 * m + 1) & 7;
+        dst[((s0 ^ chi) << 2) + in] = h01;
+        dst[((s1 ^ chi) << 2) + in] = h23;
+        dst[32 + ((s0 ^ clo) << 2) + in] = l01;           // next column (lo): 8 uint4 = 32 half2 further
+        dst[32 + ((s1 ^ clo) << 2) + in] = l23;
     }
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);   // 8 consecutive lanes cover one 32-block of one row
@@ -747,7 +758,7 @@ __device__ __forceinline__ uint32_t q4s_stage_pass(const Q4StreamLaunch& p, int 
 // (NW, MINB) = (12 warps, 2 CTAs per SM) when the shared memory of a launch fits twice on an SM -- the next launch's
 // CTA is then resident beside this one's -- and (16, 1) for activations too long for that.
 template <int G, int NW, int MINB>
-__global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4StreamLaunch p)
+__global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_constant__ Q4StreamLaunch p)
 {
     constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
     constexpr int THREADS = NW * 32;
@@ -762,10 +773,12 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
     if (lane < 2) wrp[warp][lane] = -1;
     if (tid < 2) zero_pg[tid] = make_uint4(0, 0, 0, 0);
     unsigned char* ring = smem_raw + (size_t)warp * D * STAGE_BYTES;
-    float* wpart = reinterpret_cast<float*>(smem_raw);        // [NW][2][4][32], valid after the runs are drained
     uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)NW * D * STAGE_BYTES);
     float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)p.nchunks * ncols * 128);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)p.nchunks * M * 16) + warp * Q4S_MAX_DEPTH;
+    // the warps' parked partial tiles [NW][2][4][32]: a region of their own where a CTA has the SM to itself, else
+    // the start of the ring once the runs are drained
+    float* wpart = MINB == 1 ? reinterpret_cast<float*>(bars - warp * Q4S_MAX_DEPTH + NW * Q4S_MAX_DEPTH) : reinterpret_cast<float*>(smem_raw);
 
     const int W = p.warps_total;
     const int gw = blockIdx.x * NW + warp;
@@ -852,7 +865,8 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
     // per-lane shared-memory addresses into the staged activation; lanes outside the real columns sit on a page of zeros
     const bool bvalid = g < ncols, cvalid = t < M;
     const uint32_t zero_u32 = smem_u32(zero_pg);
-    const uint32_t xs0 = bvalid ? smem_u32(xs) + (g * 4 + t) * 32 : zero_u32;
+    const uint32_t xs0 = bvalid ? smem_u32(xs) + g * 128 : zero_u32;                     // column g
+    const uint32_t xb0 = bvalid ? ((2 * t) ^ g) * 16 : 0, xb1 = bvalid ? ((2 * t + 1) ^ g) * 16 : 16;   // its slots (t, block 0 / 1)
     const uint32_t cs0 = cvalid ? smem_u32(cs) + t * 16 : zero_u32;
     const uint32_t xstep = bvalid ? ncols * 128 : 0;          // bytes per chunk
     const uint32_t cstep = cvalid ? M * 16 : 0;
@@ -871,6 +885,11 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
         const int r0 = tile_rp * gpr;
         if (gb <= r0 && r0 + gpr <= ge) {
             q4s_store_tile(p, v, tile_rp, lane);
+        } else if (MINB == 1) {                            // parked at once
+            const int slot = tile_rp == first_rp ? 0 : 1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = v[q];
+            if (lane == 0) wrp[warp][slot] = tile_rp;
         } else if (tile_rp == first_rp) {
             park[0][0] = v[0]; park[0][1] = v[1]; park[0][2] = v[2]; park[0][3] = v[3];
             park_rp[0] = tile_rp;
@@ -880,9 +899,16 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
         }
     };
     bool timed_out = false;
+#ifdef MPQ_TRACE
+    long long cyc_wait = 0, cyc_refill = 0, cyc_first = 0;
+    const long long cyc_loop0 = clock64();
+#endif
 
     for (int j = 0; j < ngroups; ++j) {
-        if (!mbar_wait(bars_u32 + s * 8, parity, Q4S_SPIN_LIMIT)) {
+        Q4S_CYC(c_w)
+        const bool arrived = mbar_wait(bars_u32 + s * 8, parity, Q4S_SPIN_LIMIT);
+        Q4S_CYC_ADD(cyc_wait, c_w)
+        if (!arrived) {
             // Record it, issue nothing more, and give every copy still in flight the same generous bounded wait, so
             // that none lands in shared memory after this CTA has left (if one still does not arrive, the hazard stays).
             if (lane == 0) {
@@ -897,7 +923,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
         for (int q = 0; q < G; ++q) {
             const uint4 w0 = lds128(wlane + st + q * Q4_UNIT_BYTES), w1 = lds128(wlane + st + q * Q4_UNIT_BYTES + 512);
             const uint4 sv = lds128(slane + st + q * Q4_UNIT_BYTES);
-            const uint4 bf[2] = {lds128(xsp), lds128(xsp + 16)};
+            const uint4 bf[2] = {lds128(xsp + xb0), lds128(xsp + xb1)};
             const uint4 cfu = lds128(csp);
             const float4 cf = make_float4(__uint_as_float(cfu.x), __uint_as_float(cfu.y), __uint_as_float(cfu.z), __uint_as_float(cfu.w));
             xsp += xstep;
@@ -922,6 +948,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
             }
         }
         ++cg;
+        Q4S_CYC(c_r)
         __syncwarp();
         if (lane == 0 && issued < ngroups) {               // refill the stage just drained
             mbar_expect_tx(bars_u32 + s * 8, STAGE_BYTES);
@@ -929,6 +956,11 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
             gnext += STAGE_BYTES;
             ++issued;
         }
+        __syncwarp();
+        Q4S_CYC_ADD(cyc_refill, c_r)
+#ifdef MPQ_TRACE
+        if (j == 0) cyc_first = clock64() - cyc_loop0;
+#endif
         if (cg == gpr) {                                   // row pair-tile finished
             flush(rp);
             acc[0][0] = acc[0][1] = acc[1][0] = acc[1][1] = 0.f;
@@ -940,18 +972,27 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
         if (++s == D) { s = 0; parity ^= 1u; }
     }
     if (cg != 0 && !timed_out) flush(rp);  // the run ended inside a row pair-tile
+#ifdef MPQ_TRACE
+    if (p.trace && tid == 0) {
+        unsigned long long* tr = p.trace + (size_t)blockIdx.x * 16;
+        tr[8] = (unsigned long long)(clock64() - cyc_loop0); tr[9] = (unsigned long long)cyc_wait; tr[10] = (unsigned long long)cyc_refill;
+        tr[11] = (unsigned long long)ngroups; tr[12] = (unsigned long long)cyc_first;
+    }
+#endif
     Q4S_TRACE(5)
     __syncthreads();                       // every warp has consumed every copy it issued: the ring is free
     Q4S_TRACE(6)
+    if (MINB != 1) {
 #pragma unroll
-    for (int slot = 0; slot < 2; ++slot) {
-        if (park_rp[slot] >= 0) {
+        for (int slot = 0; slot < 2; ++slot) {
+            if (park_rp[slot] >= 0) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = park[slot][q];
-            if (lane == 0) wrp[warp][slot] = park_rp[slot];
+                for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = park[slot][q];
+                if (lane == 0) wrp[warp][slot] = park_rp[slot];
+            }
         }
+        __syncthreads();
     }
-    __syncthreads();
 
     // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
     // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
@@ -984,7 +1025,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const Q4Stream
     // ---- row-parallel: add the ranks' partial outputs.  The tagged pairs need no flag and no grid
     // barrier: an element is ready when all xworld copies of it carry the tag.
     if (p.xworld > 0) {
-        const uint2* mine = p.xpeer[p.xrank];
+        const uint2* mine = p.xmine;
         const int total = p.M * p.N;
         for (int e = blockIdx.x * THREADS + tid; e < total; e += gridDim.x * THREADS) {
             float sum = 0.f;

@@ -7,7 +7,8 @@ Runs `layers` 7B-shape decode layers (QKV, O, gate+up, down; distinct weights) a
 programmatic dependent launch, exactly as the benchmark's stack does, using the diagnostic build of the
 library in which thread 0 of every CTA stamps %globaltimer when it has
   0 started, 1 computed its runs, 2 issued its first ring copies, 3 returned from griddepcontrol.wait,
-  4 staged the activation, 5 drained its own run, 6 passed the CTA barrier, 7 merged and stored its tiles.
+  4 staged the activation, 5 drained its own run, 6 passed the CTA barrier, 7 merged and stored its tiles,
+and warp 0 counts the cycles of its run: in total, waiting for its copies, and in the warp barrier + refill.
 Prints, per launch of the last layers, min / median / max over CTAs of each stamp in microseconds since
 the first stamp, so that the gaps between launches and the phases inside one can be read off.
 """
@@ -63,20 +64,25 @@ def main():
     lib.mpq_debug_trace.argtypes = [C.POINTER(C.c_int32)]
     count = C.c_int32()
     ptr = lib.mpq_debug_trace(C.byref(count))
-    arr = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint64)), shape=(64, 1024, 8)).copy()
+    arr = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint64)), shape=(64, 1024, 16)).copy()
     t0 = None
     prev_done = None
     for i in range(max(0, n - 8), n):
         slot = (n + i) % 64
         N, K = shapes[i]
         nct = int((arr[slot, :, 0] > 0).sum())
-        a = arr[slot, :nct, :].astype(np.int64)
+        a = arr[slot, :nct, :8].astype(np.int64)
+        cyc = arr[slot, :nct, 8:13].astype(np.int64)
         if t0 is None:
             t0 = a[:, 0].min()
         a = a - t0
         cols = " ".join(f"{nm} {a[:, k].min() / 1e3:.2f}/{np.median(a[:, k]) / 1e3:.2f}/{a[:, k].max() / 1e3:.2f}" for k, nm in enumerate(NAMES))
         gap = "" if prev_done is None else f" | last CTA done -> previous launch's last done: {(a[:, 7].max() - prev_done) / 1e3:.2f} us"
         print(f"launch {i} {N}x{K} M={args.m} ctas {nct}: {cols}{gap}")
+        ng = np.maximum(cyc[:, 3], 1)
+        print(f"    warp 0 of each CTA, cycles (median over CTAs): whole run {np.median(cyc[:, 0]):.0f} for {np.median(ng):.0f} groups = "
+              f"{np.median(cyc[:, 0] / ng):.0f} per group; waiting for copies {np.median(cyc[:, 1] / ng):.0f} per group; "
+              f"warp barrier + refill {np.median(cyc[:, 2] / ng):.0f} per group; first group {np.median(cyc[:, 4]):.0f}")
         prev_done = a[:, 7].max()
     ctx.check(lib.mpq_context_poll_status(ctx.h))
 

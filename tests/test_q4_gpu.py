@@ -239,14 +239,40 @@ def test_host_buffer_entry_point(ctx, orc):
     assert orc.rel_err(got, orc.q4_matmul_f64(codes, scales, x))[1] < TOL
 
 
-def test_general_kernel_covers_small_m_too(orc):
-    """With the streaming kernel switched off, every M runs through the phase-staged kernel (all three MMA tile counts)."""
+def test_rectangle_kernel_covers_every_row_count(orc):
+    """With the streaming kernel switched off, every M runs through the rectangle kernel (all four MMA tile counts,
+    one and several K slices, tile groups with and without shared tiles)."""
     import makepad_b200
     os.environ["MPQ_Q4_STREAM"] = "0"
     try:
         c2 = makepad_b200.Context(0)
     finally:
         del os.environ["MPQ_Q4_STREAM"]
+    for (N, K) in [(40, 160), (257, 1120), (512, 4096), (4096, 11008), (96, 28672), (20000, 64)]:
+        codes, scales = synth.q4_weight(N, K, seed=5)
+        w = makepad_b200.Q4Weight(c2, codes, scales)
+        for M in (1, 2, 4, 5, 8, 11, 12, 13, 16, 19):
+            x = synth.activations(M, K, seed=6)
+            got = _forward(c2, w, x)
+            ref = orc.q4_matmul_f64(codes, scales, x)
+            rep = orc.err_report(got, ref)
+            assert rep["floored_1e-2_rms"] < TOL and rep["max_abs_over_rms"] < 2e-5, (N, K, M, rep)
+            assert np.array_equal(got, _forward(c2, w, x))          # bit-identical between runs
+        w.destroy()
+    assert c2.lib.mpq_context_poll_status(c2.h) == _lib.OK
+    c2.close()
+
+
+def test_general_kernel_covers_small_m_too(orc):
+    """With the streaming and rectangle kernels switched off, every M runs through the phase-staged kernel (all three MMA tile counts)."""
+    import makepad_b200
+    os.environ["MPQ_Q4_STREAM"] = "0"
+    os.environ["MPQ_Q4_RECT"] = "0"
+    try:
+        c2 = makepad_b200.Context(0)
+    finally:
+        del os.environ["MPQ_Q4_STREAM"]
+        del os.environ["MPQ_Q4_RECT"]
     for (N, K) in [(40, 160), (512, 4096), (4096, 11008)]:
         codes, scales = synth.q4_weight(N, K, seed=1)
         w = makepad_b200.Q4Weight(c2, codes, scales)

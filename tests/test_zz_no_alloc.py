@@ -37,9 +37,15 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
             ctx.check(lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(x.data_ptr()), M, C.c_void_p(want.data_ptr()), s))
             torch.cuda.synchronize()
             assert int(status.item()) == 0
-            assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
             ref = orc.q4_matmul_f64(codes, scales, x.cpu().numpy())
+            assert torch.equal(outs[0], outs[1])                     # the second call found the array as clean as the first
+            if M <= 4:                                               # the same kernel, the same split into runs: the same bits
+                assert torch.equal(outs[0], want)
+            else:                                                    # other kernels above four rows: equal to rounding
+                rms = float(np.sqrt(np.mean(ref * ref)))
+                assert (outs[0] - want).abs().max().item() < 2e-5 * rms
             assert orc.rel_err(want.cpu().numpy(), ref)[1] < 1e-3
+            assert orc.rel_err(outs[0].cpu().numpy(), ref)[1] < 1e-3
         w.destroy()
     # NULL status pointer is accepted; bad arguments are rejected like the ordinary entry point's
     codes, scales = synth.q4_weight(64, 128, seed=33)
