@@ -38,16 +38,15 @@ struct mpq_context {
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
+    int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, 1 or 2
     uint2* q4_partials;
     int q4_partials_ctas;
     int* q4_status;
     bool q4_stream;           // use the streaming kernel where the activation fits in shared memory
     bool q4_tile_mode;        // let CTAs own whole row pair-tiles when the matrix has enough of them
-    bool q4_coresident;       // size a launch for half an SM where the activation allows it
     int q4_group;             // chunks per bulk copy of the streaming kernel: 0 = choose, 1 or 2
     int q4_depth;             // most ring stages per warp
-    int q4_depth_full;        // ... of a CTA that has an SM to itself
-    int q4_pre;               // stages copied before the dependency resolves (-1 = choose)
+    int q4_pre;               // stages copied before the dependency resolves (the rest right after the activation loads)
     bool q4_slab4;            // M > 4 as slabs of four rows through the streaming kernel
     Nvfp4Scratch fp4;
 };
@@ -153,18 +152,16 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_variant = (e && e[0] == '1') ? 1 : 0;
     e = getenv("MPQ_Q4_STREAM");
     c->q4_stream = !(e && e[0] == '0');
-    e = getenv("MPQ_Q4_CORESIDENT");
-    c->q4_coresident = e && e[0] == '1';          // measured slower than one CTA per SM so far: opt-in
     e = getenv("MPQ_Q4_GROUP");
     c->q4_group = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_DEPTH");
-    c->q4_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 8;
-    e = getenv("MPQ_Q4_DEPTH_FULL");
-    c->q4_depth_full = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 2;
+    c->q4_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_PRE");
-    c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : -1;
+    c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : 1;
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_RECT_DEPTH");
+    c->q4_rect_depth = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_SLAB4");
     c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
@@ -418,60 +415,42 @@ static int32_t q4_stream_scratch(mpq_context* ctx, int ctas)
 }
 
 // The streaming kernel applies when M <= 4 and the staged activation plus a ring fit in shared memory.
-// Preferred form: a launch takes less than half of an SM (shared memory, and 64 registers per thread), so
-// that the next launch's CTA is resident -- and prefetching -- beside this one; else one CTA per SM.
-struct Q4StreamPlan { int depth, G, nw, minb, pre; size_t smem; };
+struct Q4StreamPlan { int depth, G, pre; size_t smem; };
 static const size_t Q4S_STATIC_SMEM = 512;                 // s_max, wrp, zero page, rounded up
 static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4StreamPlan* pl)
 {
     if (!ctx->q4_stream || M > 4) return false;
-    // the ring with the most bytes that fits (ties: the larger copies), at least dmin stages deep
-    auto fit = [&](int nw, size_t budget, int dmax, int dmin) {
-        // activation fragments + corrections + barriers (+ the parked partial tiles, a region of their own in the one-CTA form)
-        const size_t fixed = (size_t)q.nchunks * 256 * M + (size_t)q.nchunks * 16 * M + (size_t)nw * Q4S_MAX_DEPTH * 8 +
-                             (nw == Q4S_WARPS_FULL ? (size_t)nw * 2 * 4 * 32 * 4 : 0);
-        size_t best = 0;
-        pl->nw = nw;
-        for (int G = 2; G >= 1; --G) {
-            if (ctx->q4_group && G != ctx->q4_group) continue;
-            const size_t stage = (size_t)nw * G * Q4_UNIT_BYTES;
-            if (fixed + stage * dmin > budget) continue;
-            const int d = (int)std::min<size_t>((size_t)dmax, (budget - fixed) / stage);
-            if (stage * d > best) { best = stage * d; pl->G = G; pl->depth = d; pl->smem = fixed + stage * d; }
-        }
-        return best != 0;
-    };
-    // an SM has 228 KiB of shared memory, a CTA may use 227 KiB, and the system reserves 1 KiB per resident CTA
-    const size_t half = (size_t)114 * 1024 - 1024 - Q4S_STATIC_SMEM;
-    const size_t full = (size_t)227 * 1024 - Q4S_STATIC_SMEM;
-    const int dmax = std::min(ctx->q4_depth, Q4S_MAX_DEPTH);
-    if (ctx->q4_coresident && fit(Q4S_WARPS_HALF, half, dmax, 2)) {
-        pl->minb = 2;
-        pl->pre = ctx->q4_pre < 0 ? pl->depth : ctx->q4_pre;
-        return true;
-    }
-    if (fit(Q4S_WARPS_FULL, full, std::min(dmax, ctx->q4_depth_full), 1)) {
-        pl->minb = 1;
-        pl->pre = ctx->q4_pre < 0 ? 1 : ctx->q4_pre;
+    // activation fragments + corrections + barriers + the parked partial tiles
+    const size_t fixed = (size_t)q.nchunks * 256 * M + (size_t)q.nchunks * 16 * M + (size_t)Q4S_WARPS * Q4S_MAX_DEPTH * 8 +
+                         (size_t)Q4S_WARPS * 2 * 4 * 32 * 4;
+    // a CTA may use 227 KiB of an SM's shared memory
+    const size_t budget = (size_t)227 * 1024 - Q4S_STATIC_SMEM;
+    for (int G = 2; G >= 1; --G) {
+        if (ctx->q4_group && G != ctx->q4_group) continue;
+        const size_t stage = (size_t)Q4S_WARPS * G * Q4_UNIT_BYTES;
+        if (fixed + stage > budget) continue;
+        pl->G = G;
+        pl->depth = (int)std::min<size_t>((size_t)std::min(ctx->q4_depth, Q4S_MAX_DEPTH), (budget - fixed) / stage);
+        pl->smem = fixed + stage * pl->depth;
+        pl->pre = std::min(ctx->q4_pre, pl->depth);
         return true;
     }
     return false;
 }
 
-template <int G, int NW, int MINB>
+template <int G>
 static cudaError_t q4_stream_launch_t(int device, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
 {
-    auto kern = q4_stream_kernel<G, NW, MINB>;
+    auto kern = q4_stream_kernel<G>;
     static PerDeviceOnce configured;                      // the attribute is per device, not per process
     if (configured.needs(device)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - Q4S_STATIC_SMEM));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         configured.mark(device);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(NW * 32);
+    cfg.blockDim = dim3(Q4S_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -489,7 +468,7 @@ static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4Stre
 {
     const int sms = ctx->prop.multiProcessorCount;
     const int groups = (int)(q.units() / pl.G);
-    const int W = (int)std::min<int64_t>((int64_t)sms * pl.nw, groups);
+    const int W = (int)std::min<int64_t>((int64_t)sms * Q4S_WARPS, groups);
     // whole row pair-tiles per CTA when there is about one per SM or more: no tile is then shared between CTAs
     p->tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
     p->nrp = q.nrp;
@@ -499,7 +478,7 @@ static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4Stre
     p->xworld = 0; p->xrank = 0; p->xslot = 0; p->xlimit = 0;
     for (int r = 0; r < 8; ++r) p->xpeer[r] = nullptr;
     p->xmine = nullptr;
-    return p->tile_mode ? std::min(sms, q.nrp) : (W + pl.nw - 1) / pl.nw;
+    return p->tile_mode ? std::min(sms, q.nrp) : (W + Q4S_WARPS - 1) / Q4S_WARPS;
 }
 
 #ifdef MPQ_TRACE
@@ -522,9 +501,7 @@ static int32_t q4_stream_enqueue(mpq_context* ctx, const Q4StreamPlan& pl, const
 #else
     const Q4StreamLaunch& p = p_in;
 #endif
-    cudaError_t e;
-    if (pl.minb == 2) e = pl.G == 2 ? q4_stream_launch_t<2, Q4S_WARPS_HALF, 2>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1, Q4S_WARPS_HALF, 2>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
-    else e = pl.G == 2 ? q4_stream_launch_t<2, Q4S_WARPS_FULL, 1>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1, Q4S_WARPS_FULL, 1>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
+    cudaError_t e = pl.G == 2 ? q4_stream_launch_t<2>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
     ctx->launches += 1;
     if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
     return MPQ_OK;
@@ -561,22 +538,27 @@ static bool q4_rect_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4RectPl
     const size_t per_chunk = (size_t)2 * mp * 128 + (size_t)2 * mp * 8;          // fragments + corrections
     const size_t wpart = (size_t)Q4R_WARPS * 2 * (4 * mt) * 32 * 4, bars = (size_t)Q4R_WARPS * Q4S_MAX_DEPTH * 8;
     const size_t total = (size_t)227 * 1024 - 512;
+    // The deeper ring first (measured: two stages per warp with more K slices beat one stage with fewer);
+    // MPQ_Q4_RECT_DEPTH pins the ring depth.
+    bool found = false;
     for (int depth = 2; depth >= 1; --depth) {
+        if (ctx->q4_rect_depth && depth != ctx->q4_rect_depth) continue;
         const size_t ring = (size_t)Q4R_WARPS * depth * Q4R_STAGE_BYTES;
         if (ring + wpart + bars + per_chunk * Q4R_G > total) continue;
         int max_slice = (int)((total - ring - wpart - bars) / per_chunk) / Q4R_G * Q4R_G;
         // K slices: as few as fit, but enough of them that tile groups x slices can cover the SMs
         int nks = (q.nchunks + max_slice - 1) / max_slice;
-        while (nks < 16 && (int64_t)q.nrp * nks < sms && q.nchunks / (nks + 1) >= 2 * Q4R_G) ++nks;
+        while (nks < 16 && (int64_t)q.nrp * nks * 10 < (int64_t)sms * 6 && q.nchunks / (nks + 1) >= 2 * Q4R_G) ++nks;
         int slice = ((q.nchunks + nks - 1) / nks + Q4R_G - 1) / Q4R_G * Q4R_G;
         nks = (q.nchunks + slice - 1) / slice;
-        pl->mt = mt; pl->depth = depth; pl->slice_chunks = slice; pl->nks = nks;
         if (nks > sms) continue;                           // (cannot happen for K below a few million)
+        if (found) continue;
+        found = true;
+        pl->mt = mt; pl->depth = depth; pl->slice_chunks = slice; pl->nks = nks;
         pl->ntg = std::max(1, std::min(q.nrp, sms / nks));
         pl->smem = ring + per_chunk * slice + wpart + bars;
-        return true;
     }
-    return false;
+    return found;
 }
 
 template <int MT>

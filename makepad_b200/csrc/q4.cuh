@@ -433,13 +433,7 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // the streaming kernel: M <= 4, whole x resident in shared memory
 // ---------------------------------------------------------------------------
 // One CTA of sixteen warps per SM and launch, no CTA-wide synchronisation
-// between staging the activation and draining the runs.  Where the activation
-// is short enough the kernel is built for 64 registers per thread and asks for
-// less than half of an SM's shared memory, so that the CTA of the NEXT launch
-// in the stream (programmatic dependent launch) is resident beside this one:
-// its start-up, barrier initialisation and the bulk copies that fill its ring
-// all run while this launch still streams, and only what depends on the
-// activation is left after griddepcontrol.wait.
+// between staging the activation and draining the runs.
 //
 // The unit stream is cut into contiguous runs of GROUPS (G consecutive chunks
 // of one row pair-tile; the layout pads K so that a group never straddles a
@@ -456,8 +450,8 @@ __global__ void __launch_bounds__(Q4_THREADS) q4_linear_kernel(const Q4Launch p)
 // to y.  A tile shared by warps of one CTA is summed through shared memory, in
 // warp order, when the CTA has drained its runs.  A tile cut by the boundary
 // between two CTAs is finished through global scratch (q4s_cross_cta).
-constexpr int Q4S_WARPS_FULL = 16;               // warps of a CTA that has an SM to itself
-constexpr int Q4S_WARPS_HALF = 12;               // warps of a CTA that shares an SM with the next launch's (85 registers each)
+constexpr int Q4S_WARPS = 16;                    // one CTA of sixteen warps per SM
+constexpr int Q4S_THREADS = Q4S_WARPS * 32;
 constexpr int Q4S_MAX_DEPTH = 8;                 // most ring stages per warp
 constexpr int Q4_GROUP_PAD = 4;                  // chunks per row pair-tile are padded to a multiple of this
 constexpr uint32_t Q4S_SPIN_LIMIT = 1u << 22;    // polls of one mbarrier before giving up
@@ -635,20 +629,19 @@ __device__ __forceinline__ void q4s_store_tile(const Q4StreamLaunch& p, const fl
 // the sum does not depend on timing, writes y, and clears the slots it consumed.  A slot is written
 // once and read once per launch, and the next launch writes only after this one has completed, so the
 // protocol needs no per-launch state (it is safe under CUDA-graph replay).
-template <int NW>
 __device__ __noinline__ void q4s_cross_cta(const Q4StreamLaunch& p, float v0, float v1, float v2, float v3, int rp, int r0,
                                            int r1, int cta_first_rp, int lane)
 {
     float v[4] = {v0, v1, v2, v3};
     const int W = p.warps_total;
-    const int c0 = q4s_owner(r0, p.groups, W) / NW;
+    const int c0 = q4s_owner(r0, p.groups, W) / Q4S_WARPS;
     if ((int)blockIdx.x != c0) {
         uint2* mine = p.partials + (((size_t)blockIdx.x * 2 + (rp == cta_first_rp ? 0 : 1)) * 32 + lane) * 4;
 #pragma unroll
         for (int q = 0; q < 4; ++q) st_tagged(mine + q, v[q], 1u);
         return;
     }
-    const int c1 = q4s_owner(r1 - 1, p.groups, W) / NW;
+    const int c1 = q4s_owner(r1 - 1, p.groups, W) / Q4S_WARPS;
     // every later CTA starts its run inside this tile, so the tile is its first one (slot 0)
     const uint2* src = p.partials + (((size_t)(c0 + 1) * 2) * 32 + lane) * 4;
     for (int c = c0 + 1; c <= c1; c += 4) {                // four contributors' loads in flight at a time
@@ -753,15 +746,12 @@ __device__ __forceinline__ uint32_t q4s_stage_pass(const Q4StreamLaunch& p, int 
     return mx;
 }
 
-// dynamic shared memory: ring [16 warps][depth][G units] | xs | cs | mbarriers; after the runs are drained the start of
-// the ring is reused for the warps' parked partial tiles.
-// (NW, MINB) = (12 warps, 2 CTAs per SM) when the shared memory of a launch fits twice on an SM -- the next launch's
-// CTA is then resident beside this one's -- and (16, 1) for activations too long for that.
-template <int G, int NW, int MINB>
-__global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_constant__ Q4StreamLaunch p)
+// dynamic shared memory: ring [16 warps][depth][G units] | xs | cs | mbarriers | wpart (the warps' parked partial tiles)
+template <int G>
+__global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const __grid_constant__ Q4StreamLaunch p)
 {
     constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
-    constexpr int THREADS = NW * 32;
+    constexpr int NW = Q4S_WARPS, THREADS = Q4S_THREADS;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ uint32_t s_max[NW];
     __shared__ int wrp[NW][2];                    // the tile index of each warp's parked partial tiles, -1 if none
@@ -776,9 +766,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_c
     uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)NW * D * STAGE_BYTES);
     float4* cs = reinterpret_cast<float4*>(reinterpret_cast<unsigned char*>(xs) + (size_t)p.nchunks * ncols * 128);
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(cs) + (size_t)p.nchunks * M * 16) + warp * Q4S_MAX_DEPTH;
-    // the warps' parked partial tiles [NW][2][4][32]: a region of their own where a CTA has the SM to itself, else
-    // the start of the ring once the runs are drained
-    float* wpart = MINB == 1 ? reinterpret_cast<float*>(bars - warp * Q4S_MAX_DEPTH + NW * Q4S_MAX_DEPTH) : reinterpret_cast<float*>(smem_raw);
+    float* wpart = reinterpret_cast<float*>(bars - warp * Q4S_MAX_DEPTH + NW * Q4S_MAX_DEPTH);     // [NW][2][4][32]
 
     const int W = p.warps_total;
     const int gw = blockIdx.x * NW + warp;
@@ -876,26 +864,17 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_c
     int s = 0;
     uint32_t parity = 0;
 
-    // A tile wholly inside this warp's run goes straight to y.  A tile it shares with other warps (at most its first
-    // and its last one) is kept in registers until the whole CTA has drained its runs, then parked in shared memory.
-    float park[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    int park_rp[2] = {-1, -1};
+    // a tile wholly inside this warp's run goes straight to y; a tile it shares (at most its first and its last) is parked
     auto flush = [&](int tile_rp) {
         float v[4] = {acc[0][0] * fA, acc[0][1] * fB, acc[1][0] * fA, acc[1][1] * fB};
         const int r0 = tile_rp * gpr;
         if (gb <= r0 && r0 + gpr <= ge) {
             q4s_store_tile(p, v, tile_rp, lane);
-        } else if (MINB == 1) {                            // parked at once
+        } else {
             const int slot = tile_rp == first_rp ? 0 : 1;
 #pragma unroll
             for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = v[q];
             if (lane == 0) wrp[warp][slot] = tile_rp;
-        } else if (tile_rp == first_rp) {
-            park[0][0] = v[0]; park[0][1] = v[1]; park[0][2] = v[2]; park[0][3] = v[3];
-            park_rp[0] = tile_rp;
-        } else {
-            park[1][0] = v[0]; park[1][1] = v[1]; park[1][2] = v[2]; park[1][3] = v[3];
-            park_rp[1] = tile_rp;
         }
     };
     bool timed_out = false;
@@ -980,24 +959,13 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_c
     }
 #endif
     Q4S_TRACE(5)
-    __syncthreads();                       // every warp has consumed every copy it issued: the ring is free
+    __syncthreads();
     Q4S_TRACE(6)
-    if (MINB != 1) {
-#pragma unroll
-        for (int slot = 0; slot < 2; ++slot) {
-            if (park_rp[slot] >= 0) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) wpart[((warp * 2 + slot) * 4 + q) * 32 + lane] = park[slot][q];
-                if (lane == 0) wrp[warp][slot] = park_rp[slot];
-            }
-        }
-        __syncthreads();
-    }
 
     // ---- tiles shared between warps: add the parked partials in warp order.  Segment (w, slot) opens a
     // tile if the valid segment before it belongs to another tile; its warp then sums the following ones.
     const int cta_first_rp = cta_gb / gpr;
-    const int entry = lane < 2 * NW ? wrp[lane >> 1][lane & 1] : -1;   // lane i holds segment i = (warp i/2, slot i%2)
+    const int entry = wrp[lane >> 1][lane & 1];             // lane i holds segment i = (warp i/2, slot i%2)
 #pragma unroll
     for (int slot = 0; slot < 2; ++slot) {
         const int idx0 = warp * 2 + slot;
@@ -1016,7 +984,7 @@ __global__ void __launch_bounds__(NW * 32, MINB) q4_stream_kernel(const __grid_c
             const float v[4] = {v0, v1, v2, v3};
             q4s_store_tile(p, v, my, lane);
         } else {
-            q4s_cross_cta<NW>(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
+            q4s_cross_cta(p, v0, v1, v2, v3, my, r0, r1, cta_first_rp, lane);
         }
     }
 
