@@ -16,6 +16,11 @@ pub const MPQ_ERR_CUDA: i32 = -4;
 pub const MPQ_ERR_UNSUPPORTED: i32 = -5;
 pub const MPQ_ERR_PEER_TIMEOUT: i32 = -6;
 pub const MPQ_ERR_STATE: i32 = -7;
+pub const MPQ_ERR_FORMAT: i32 = -8;
+pub const MPQ_ERR_IO: i32 = -9;
+
+pub const MPQ_FILE_CANONICAL: i32 = 1;
+pub const MPQ_FILE_DEVICE: i32 = 2;
 
 pub const MPQ_FMT_Q4: i32 = 1;
 pub const MPQ_FMT_NVFP4: i32 = 2;
@@ -38,6 +43,21 @@ pub struct mpq_device_info {
     pub total_mem_bytes: i64,
     pub sm_clock_khz: i32,
     pub mem_clock_khz: i32,
+}
+
+#[repr(C)]
+#[derive(Clone, Copy, Default, Debug)]
+pub struct mpq_file_info_t {
+    pub kind: i32,
+    pub fmt: i32,
+    pub layout_version: i32,
+    pub reserved: i32,
+    pub N: i64,
+    pub K: i64,
+    pub bytes_a: i64,
+    pub bytes_b: i64,
+    pub tensor_scale: f32,
+    pub reserved2: i32,
 }
 
 extern "C" {
@@ -71,10 +91,19 @@ pub struct LibMpq {
     pub mpq_exchange_attach_pointers: unsafe extern "C" fn(*mut mpq_exchange, *const *mut c_void) -> i32,
     pub mpq_exchange_buffer: unsafe extern "C" fn(*mut mpq_exchange, *mut *mut c_void, *mut i64) -> i32,
     pub mpq_exchange_set_wait_limit: unsafe extern "C" fn(*mut mpq_exchange, u32) -> i32,
+    pub mpq_exchange_graph_check: unsafe extern "C" fn(*mut mpq_exchange) -> i32,
     pub mpq_exchange_destroy: unsafe extern "C" fn(*mut mpq_exchange) -> i32,
     pub mpq_q4_linear_forward_allreduce: unsafe extern "C" fn(*mut mpq_context, *const mpq_weight, *mut mpq_exchange, *const f32, i64, *mut f32, *mut c_void) -> i32,
     pub mpq_nvfp4_gemm_forward: unsafe extern "C" fn(*mut mpq_context, *const mpq_weight, *const u8, *const u8, f32, i64, *mut u16, *mut c_void) -> i32,
     pub mpq_nvfp4_dequantize: unsafe extern "C" fn(*mut mpq_context, i64, i64, *const u8, *const u8, f32, *mut f32, *mut c_void) -> i32,
+    pub mpq_nvfp4_quantize_activations: unsafe extern "C" fn(*mut mpq_context, *const c_void, i32, i64, i64, f32, *mut u8, *mut u8, *mut c_void) -> i32,
+    pub mpq_file_info: unsafe extern "C" fn(*const c_char, *mut mpq_file_info_t) -> i32,
+    pub mpq_canonical_save: unsafe extern "C" fn(*const c_char, i32, i64, i64, *const u8, *const c_void, f32) -> i32,
+    pub mpq_canonical_load: unsafe extern "C" fn(*const c_char, *mut u8, i64, *mut c_void, i64, *mut f32) -> i32,
+    pub mpq_weight_save: unsafe extern "C" fn(*mut mpq_context, *const mpq_weight, *const c_char) -> i32,
+    pub mpq_weight_load: unsafe extern "C" fn(*mut mpq_context, *const c_char, *mut *mut mpq_weight) -> i32,
+    pub mpq_probe_hbm_read: unsafe extern "C" fn(*mut mpq_context, *const c_void, i64, *mut u32, *mut c_void) -> i32,
+    pub mpq_probe_fp4_mma: unsafe extern "C" fn(*mut mpq_context, i32, *mut f64, *mut c_void) -> i32,
     _keep_module_alive: *mut c_void,
 }
 
@@ -123,10 +152,19 @@ impl LibMpq {
                 mpq_exchange_attach_pointers: sym!(h, "mpq_exchange_attach_pointers"),
                 mpq_exchange_buffer: sym!(h, "mpq_exchange_buffer"),
                 mpq_exchange_set_wait_limit: sym!(h, "mpq_exchange_set_wait_limit"),
+                mpq_exchange_graph_check: sym!(h, "mpq_exchange_graph_check"),
                 mpq_exchange_destroy: sym!(h, "mpq_exchange_destroy"),
                 mpq_q4_linear_forward_allreduce: sym!(h, "mpq_q4_linear_forward_allreduce"),
                 mpq_nvfp4_gemm_forward: sym!(h, "mpq_nvfp4_gemm_forward"),
                 mpq_nvfp4_dequantize: sym!(h, "mpq_nvfp4_dequantize"),
+                mpq_nvfp4_quantize_activations: sym!(h, "mpq_nvfp4_quantize_activations"),
+                mpq_file_info: sym!(h, "mpq_file_info"),
+                mpq_canonical_save: sym!(h, "mpq_canonical_save"),
+                mpq_canonical_load: sym!(h, "mpq_canonical_load"),
+                mpq_weight_save: sym!(h, "mpq_weight_save"),
+                mpq_weight_load: sym!(h, "mpq_weight_load"),
+                mpq_probe_hbm_read: sym!(h, "mpq_probe_hbm_read"),
+                mpq_probe_fp4_mma: sym!(h, "mpq_probe_fp4_mma"),
                 _keep_module_alive: h,
             })
         }

@@ -19,6 +19,7 @@
 #include "per_device.h"
 #include "q4.cuh"
 #include "q4_rect.cuh"
+#include "q4_umma.cuh"
 
 using namespace mpq;
 
@@ -35,6 +36,9 @@ struct mpq_context {
     size_t hx_bytes, hy_bytes;
     // scratch of the streaming Q4 kernel: tagged partial tiles of row pair-tiles cut by a boundary
     // between two CTAs' runs (two slots per CTA; write-once / read-once per launch), one status word
+    unsigned char* q4u_xs;    // staged activations of the tcgen05 kernel (grown on demand), then 64 floats of row scales
+    size_t q4u_xs_bytes;
+    int q4_umma_min;          // fewest activation rows routed to the tcgen05 kernel (0 = never)
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
@@ -134,6 +138,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->hx = c->hy = nullptr;
     c->hx_bytes = c->hy_bytes = 0;
     c->q4_partials = nullptr;
+    c->q4u_xs = nullptr;
+    c->q4u_xs_bytes = 0;
     c->q4_rect_partial = nullptr;
     c->q4_rect_partial_bytes = 0;
     c->q4_partials_ctas = 0;
@@ -158,6 +164,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 2;
     e = getenv("MPQ_Q4_PRE");
     c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : 1;
+    e = getenv("MPQ_Q4_UMMA_MIN");
+    c->q4_umma_min = e ? atoi(e) : 33;         // measured: the rectangle kernel (two passes) is as fast up to 32 rows
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_RECT_DEPTH");
@@ -177,6 +185,7 @@ extern "C" int32_t mpq_context_destroy(mpq_context* ctx)
     cudaFree(ctx->hx);
     cudaFree(ctx->hy);
     cudaFree(ctx->q4_partials);
+    cudaFree(ctx->q4u_xs);
     cudaFree(ctx->q4_rect_partial);
     cudaFree(ctx->q4_status);
     ctx->fp4.release();
@@ -643,6 +652,111 @@ static int32_t q4_rect_forward(mpq_context* ctx, const Q4Dev& q, const Q4RectPla
     return MPQ_OK;
 }
 
+// ---------------------------------------------------------------------------
+// the tcgen05 kernel: 5..64 rows per pass, weights read once
+// ---------------------------------------------------------------------------
+static int32_t q4_partial_scratch(mpq_context* ctx, size_t need)
+{
+    if (ctx->q4_rect_partial_bytes < need) {
+        CU_TRY(ctx, cudaDeviceSynchronize());          // nobody may still be using the old array
+        cudaFree(ctx->q4_rect_partial);
+        ctx->q4_rect_partial = nullptr;
+        ctx->q4_rect_partial_bytes = 0;
+        CU_TRY(ctx, cudaMalloc(&ctx->q4_rect_partial, need));
+        ctx->q4_rect_partial_bytes = need;
+    }
+    return MPQ_OK;
+}
+
+static cudaError_t launch_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* at, bool pdl)
+{
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1u : 0u;
+    return cudaSuccess;
+}
+
+static int32_t q4_umma_forward(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
+{
+    const int sms = ctx->prop.multiProcessorCount;
+    const int Mp = (M + 15) / 16 * 16;
+    int32_t st = q4_status_word(ctx);
+    if (st) return st;
+    // staged activations: per chunk a hi and a lo tile of Mp rows x 128 bytes, then the row scales
+    const size_t xs_bytes = (size_t)q.nchunks * 2 * Mp * 128, need = xs_bytes + 64 * sizeof(float);
+    if (ctx->q4u_xs_bytes < need) {
+        CU_TRY(ctx, cudaDeviceSynchronize());
+        cudaFree(ctx->q4u_xs);
+        ctx->q4u_xs = nullptr;
+        ctx->q4u_xs_bytes = 0;
+        CU_TRY(ctx, cudaMalloc(&ctx->q4u_xs, need));
+        ctx->q4u_xs_bytes = need;
+    }
+    float* inv_sc = reinterpret_cast<float*>(ctx->q4u_xs + (ctx->q4u_xs_bytes - 64 * sizeof(float)));
+    // work items: batches of T weight groups (they share the activation tiles) x K ranges; the split that fills the SMs best
+    const int ng = (q.nrp + 3) / 4;
+    int bestT = 1, bestK = 1;
+    double best = -1.0;
+    const int stack = Mp <= 32 ? 1 : 0;                // accumulators of 2 Mp columns where four of them fit in 256
+    for (int T = std::min(Q4U_MAX_T, 256 / (stack ? 2 * Mp : Mp)); T >= 1; --T)
+        for (int nks = 1; nks <= 8; ++nks) {
+            if (nks > 1 && q.nchunks / nks < 8) break;
+            const int items = (ng + T - 1) / T * nks;
+            const int waves = (items + sms - 1) / sms;
+            // efficiency of the SM use, with a mild preference for wide batches (less activation traffic) and few K ranges
+            const double eff = (double)items / ((double)waves * sms) * (1.0 - 0.02 * (Q4U_MAX_T - T)) * (1.0 - 0.01 * (nks - 1));
+            if (eff > best) { best = eff; bestT = T; bestK = nks; }
+        }
+    const int slice = (q.nchunks + bestK - 1) / bestK;
+    const int nks = (q.nchunks + slice - 1) / slice;
+    if (nks > 1 && (st = q4_partial_scratch(ctx, (size_t)nks * M * q.N * sizeof(float)))) return st;
+
+    cudaLaunchAttribute at[1];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)Mp);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    launch_pdl(cfg, at, ctx->pdl);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, q4u_xstage_kernel, x, M, Mp, (int)q.K, q.nchunks, ctx->q4u_xs, inv_sc);
+    ctx->launches += 1;
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4u_xstage_kernel launch failed: %s", cudaGetErrorString(e));
+
+    Q4ULaunch p;
+    p.stream = q.stream; p.XS = ctx->q4u_xs; p.inv_sc = inv_sc; p.Y = y; p.partial = ctx->q4_rect_partial;
+    p.M = M; p.Mp = Mp; p.N = (int)q.N; p.ldy = ldy; p.nchunks = q.nchunks; p.nrp = q.nrp; p.ngroups = ng;
+    p.stack = stack;
+    p.T = bestT; p.nbatches = (ng + bestT - 1) / bestT; p.nks = nks; p.slice_chunks = slice; p.status = ctx->q4_status;
+    // at least 116 KiB, so that two CTAs never share an SM (each allocates all of its tensor memory)
+    const size_t smem = std::max<size_t>((size_t)Q4U_XSTAGES * 2 * Mp * 128 + (size_t)Q4U_WSTAGES * Q4U_WSTAGE_BYTES + 512 + 1024, (size_t)116 * 1024);
+    static PerDeviceOnce configured;
+    if (configured.needs(ctx->device)) {
+        CU_TRY(ctx, cudaFuncSetAttribute(q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024)));
+        configured.mark(ctx->device);
+    }
+    cfg = {};
+    cfg.gridDim = dim3((unsigned)std::min(p.nbatches * p.nks, sms));
+    cfg.blockDim = dim3(Q4U_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    launch_pdl(cfg, at, ctx->pdl);
+    e = cudaLaunchKernelEx(&cfg, q4_umma_kernel, p);
+    ctx->launches += 1;
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_umma_kernel launch failed: %s", cudaGetErrorString(e));
+    if (nks > 1) {
+        cfg = {};
+        const int64_t total = (int64_t)M * q.N;
+        cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)sms * 8));
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        launch_pdl(cfg, at, ctx->pdl);
+        e = cudaLaunchKernelEx(&cfg, q4_rect_reduce_kernel, (const float*)ctx->q4_rect_partial, nks, M, (int)q.N, y, ldy);
+        ctx->launches += 1;
+        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_rect_reduce_kernel launch failed: %s", cudaGetErrorString(e));
+    }
+    return MPQ_OK;
+}
+
 // One launch for a slab of M <= 16 activation rows.
 static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s);
 static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
@@ -702,6 +816,14 @@ static int q4_slab_rows(const mpq_context* ctx, const Q4Dev& q, int64_t M)
 static int32_t q4_forward_checked(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M, float* y_dev,
                                   int64_t ldy, cudaStream_t s)
 {
+    if (ctx->q4_umma_min > 0 && M >= ctx->q4_umma_min) {       // slabs of up to 64 rows on the tcgen05 path
+        for (int64_t m0 = 0; m0 < M; m0 += 64) {
+            int m = (int)std::min<int64_t>(64, M - m0);
+            int32_t st = q4_umma_forward(ctx, w->q4, x_dev + (size_t)m0 * w->q4.K, m, y_dev + (size_t)m0 * ldy, ldy, s);
+            if (st) return st;
+        }
+        return MPQ_OK;
+    }
     const int slab = q4_slab_rows(ctx, w->q4, M);
     for (int64_t m0 = 0; m0 < M; m0 += slab) {
         int m = (int)std::min<int64_t>(slab, M - m0);

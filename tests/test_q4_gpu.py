@@ -263,6 +263,39 @@ def test_rectangle_kernel_covers_every_row_count(orc):
     c2.close()
 
 
+def test_tcgen05_kernel_covers_every_row_count(orc):
+    """The tcgen05 kernel (by default used from 33 activation rows up) forced on from 5 rows: every accumulator width, both
+    MMA forms (one or two MMAs for the hi part), one and several K ranges, several K segments, ragged last groups; outputs
+    beyond the matrix stay untouched and two runs give the same bits."""
+    import makepad_b200
+    torch = _torch()
+    os.environ["MPQ_Q4_UMMA_MIN"] = "5"
+    try:
+        c2 = makepad_b200.Context(0)
+    finally:
+        del os.environ["MPQ_Q4_UMMA_MIN"]
+    for (N, K) in [(40, 160), (257, 1120), (512, 4096), (4096, 11008), (96, 28672), (20000, 64)]:
+        codes, scales = synth.q4_weight(N, K, seed=15)
+        w = makepad_b200.Q4Weight(c2, codes, scales)
+        for M in (5, 16, 17, 32, 33, 48, 49, 64, 70):
+            x = synth.activations(M, K, seed=16)
+            buf = torch.full((M * N + 256,), 777.0, device="cuda")
+            y = buf[128:128 + M * N].view(M, N)
+            xd = torch.from_numpy(x).cuda()
+            makepad_b200.QuantLinear(w).forward(xd, out=y)
+            torch.cuda.synchronize()
+            ref = orc.q4_matmul_f64(codes, scales, x)
+            rep = orc.err_report(y.cpu().numpy(), ref)
+            assert rep["floored_1e-2_rms"] < TOL and rep["max_abs_over_rms"] < 2e-5, (N, K, M, rep)
+            assert (buf[:128] == 777.0).all() and (buf[128 + M * N:] == 777.0).all()
+            y2 = makepad_b200.QuantLinear(w)(xd)
+            torch.cuda.synchronize()
+            assert torch.equal(y, y2)
+        w.destroy()
+    assert c2.lib.mpq_context_poll_status(c2.h) == _lib.OK
+    c2.close()
+
+
 def test_general_kernel_covers_small_m_too(orc):
     """With the streaming and rectangle kernels switched off, every M runs through the phase-staged kernel (all three MMA tile counts)."""
     import makepad_b200
