@@ -260,6 +260,50 @@ def extras(ctx, peak):
     return out
 
 
+def one_kernel(spec: str, reps: int):
+    """`--one q4:NxK:M` or `--one nvfp4:MxNxK`: a few launches of one operator on seeded synthetic data (four weight copies
+    for Q4, so that launches miss L2), event-timed; the command the ncu captures under profiles/ run."""
+    import ctypes as C
+    import torch
+    import makepad_b200
+    from makepad_b200.decode_stack import q4_bytes, random_q4_weight_on_device
+    kind, dims = spec.split(":", 1)
+    ctx = makepad_b200.Context(0)
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if kind == "q4":
+        shape, M = dims.split(":")
+        N, K = (int(v) for v in shape.split("x"))
+        M = int(M)
+        ws = [random_q4_weight_on_device(ctx, N, K, 100 + i) for i in range(4)]
+        x = torch.randn(M, K, device="cuda"); y = torch.empty(M, N, device="cuda")
+        def run():
+            for w in ws:
+                ctx.check(ctx.lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(x.data_ptr()), M, C.c_void_p(y.data_ptr()), s))
+        work, unit = q4_bytes(N, K, M) * len(ws), "GB/s"
+    else:
+        M, N, K = (int(v) for v in dims.split("x"))
+        g = torch.Generator(device="cuda"); g.manual_seed(3)
+        a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+        bq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+        sfa = (torch.randn((M, K // 16), device="cuda", generator=g).abs() * 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
+        sfb = (torch.randn((N, K // 16), device="cuda", generator=g).abs() * 0.1).to(torch.float8_e4m3fn).view(torch.uint8)
+        w = makepad_b200.Nvfp4Weight(ctx, bq.cpu().numpy(), sfb.cpu().numpy(), 1.0)
+        lin = makepad_b200.QuantLinear(w)
+        c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        def run():
+            lin((a, sfa, 1.0), out=c)
+        work, unit = 2.0 * M * N * K, "TFLOP/s"
+    run(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record(); torch.cuda.synchronize()
+    ctx.check(ctx.lib.mpq_context_poll_status(ctx.h))
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    print(json.dumps({"one": spec, "us_per_pass": us, "rate": work / us / (1e3 if unit == "GB/s" else 1e6), "unit": unit, "launches": ctx.launches}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -268,7 +312,11 @@ def main():
     ap.add_argument("--impl", default="mpq", choices=["mpq", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=20)
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations (config 0, 2, 3, 4 on one GPU)")
+    ap.add_argument("--one", default=None, help="q4:NxK:M or nvfp4:MxNxK: run only this operator a few times (for profiler captures)")
+    ap.add_argument("--one-reps", type=int, default=2)
     args = ap.parse_args()
+    if args.one:
+        return one_kernel(args.one, args.one_reps)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
