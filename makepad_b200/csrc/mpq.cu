@@ -165,7 +165,7 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     e = getenv("MPQ_Q4_PRE");
     c->q4_pre = (e && e[0] >= '0' && e[0] <= '8') ? e[0] - '0' : 1;
     e = getenv("MPQ_Q4_UMMA_MIN");
-    c->q4_umma_min = e ? atoi(e) : 33;         // measured: the rectangle kernel (two passes) is as fast up to 32 rows
+    c->q4_umma_min = e ? atoi(e) : 17;         // measured: above 16 rows (two passes of the rectangle kernel) the tcgen05 kernel is faster
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_RECT_DEPTH");
@@ -491,13 +491,31 @@ static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4Stre
 }
 
 #ifdef MPQ_TRACE
-// Diagnostic build: launch i of the process stamps its CTAs' phase times into slot i % 64 of a managed array.
+// Diagnostic build: launch i of the process stamps its CTAs' phase times into slot i % 64 of a device array
+// (not managed memory: the first touch of a managed page from a kernel stalls the SM for tens of microseconds).
 static unsigned long long* g_trace = nullptr;
+static unsigned long long* g_trace_host = nullptr;
 static int g_trace_n = 0;
+static const size_t g_trace_bytes = (size_t)64 * 1024 * 16 * 8;
+static unsigned long long* trace_buffer()
+{
+    if (!g_trace) {
+        if (cudaMalloc(&g_trace, g_trace_bytes) != cudaSuccess) { g_trace = nullptr; return nullptr; }
+        cudaMemset(g_trace, 0, g_trace_bytes);
+        cudaDeviceSynchronize();
+    }
+    return g_trace;
+}
+// Waits for the device and returns a host copy of the array (valid until the next call).
 extern "C" unsigned long long* mpq_debug_trace(int32_t* launches)
 {
     if (launches) *launches = g_trace_n;
-    return g_trace;
+    if (!g_trace) return nullptr;
+    if (!g_trace_host) g_trace_host = static_cast<unsigned long long*>(malloc(g_trace_bytes));
+    if (!g_trace_host) return nullptr;
+    cudaDeviceSynchronize();
+    cudaMemcpy(g_trace_host, g_trace, g_trace_bytes, cudaMemcpyDeviceToHost);
+    return g_trace_host;
 }
 #endif
 
@@ -505,8 +523,7 @@ static int32_t q4_stream_enqueue(mpq_context* ctx, const Q4StreamPlan& pl, const
 {
 #ifdef MPQ_TRACE
     Q4StreamLaunch p = p_in;
-    if (!g_trace && cudaMallocManaged(&g_trace, (size_t)64 * 1024 * 16 * 8) != cudaSuccess) g_trace = nullptr;
-    p.trace = (g_trace && grid <= 1024) ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 16 : nullptr;
+    p.trace = (trace_buffer() && grid <= 1024) ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 16 : nullptr;
 #else
     const Q4StreamLaunch& p = p_in;
 #endif
@@ -694,27 +711,24 @@ static int32_t q4_umma_forward(mpq_context* ctx, const Q4Dev& q, const float* x,
         ctx->q4u_xs_bytes = need;
     }
     float* inv_sc = reinterpret_cast<float*>(ctx->q4u_xs + (ctx->q4u_xs_bytes - 64 * sizeof(float)));
-    // work items: batches of T weight groups (they share the activation tiles) x K ranges; the split that fills the SMs best
+    // equal ranges of the (batch, chunk) sequence, one per SM; at least four chunks each (a piece costs a partial slice)
     const int ng = (q.nrp + 3) / 4;
-    int bestT = 1, bestK = 1;
-    double best = -1.0;
-    const int stack = Mp <= 32 ? 1 : 0;                // accumulators of 2 Mp columns where four of them fit in 256
-    for (int T = std::min(Q4U_MAX_T, 256 / (stack ? 2 * Mp : Mp)); T >= 1; --T)
-        for (int nks = 1; nks <= 8; ++nks) {
-            if (nks > 1 && q.nchunks / nks < 8) break;
-            const int items = (ng + T - 1) / T * nks;
-            const int waves = (items + sms - 1) / sms;
-            // efficiency of the SM use, with a mild preference for wide batches (less activation traffic) and few K ranges
-            const double eff = (double)items / ((double)waves * sms) * (1.0 - 0.02 * (Q4U_MAX_T - T)) * (1.0 - 0.01 * (nks - 1));
-            if (eff > best) { best = eff; bestT = T; bestK = nks; }
-        }
-    const int slice = (q.nchunks + bestK - 1) / bestK;
-    const int nks = (q.nchunks + slice - 1) / slice;
-    if (nks > 1 && (st = q4_partial_scratch(ctx, (size_t)nks * M * q.N * sizeof(float)))) return st;
+    const int nbatches = (ng + Q4U_TEAMS - 1) / Q4U_TEAMS;
+    const int stack = Mp <= 32 ? 1 : 0;                // accumulators of 2 Mp columns where they fit in a team's 64
+    const long long total = (long long)nbatches * q.nchunks;
+    int W = (int)std::max<long long>((total + sms - 1) / sms, std::min<long long>(4, total));
+    const int grid = (int)((total + W - 1) / W);
+    int maxp = 1;
+    for (int bb = 0; bb < nbatches; ++bb) {
+        int pf, pl;
+        q4u_pieces(bb, q.nchunks, W, &pf, &pl);
+        maxp = std::max(maxp, pl - pf + 1);
+    }
+    if (maxp > 1 && (st = q4_partial_scratch(ctx, (size_t)maxp * M * q.N * sizeof(float)))) return st;
 
     cudaLaunchAttribute at[1];
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)Mp);
+    cfg.gridDim = dim3((unsigned)Mp, (unsigned)std::max(1, std::min(8, 2 * sms / Mp)));     // a row is shared by several CTAs: about two per SM
     cfg.blockDim = dim3(256);
     cfg.stream = s;
     launch_pdl(cfg, at, ctx->pdl);
@@ -725,17 +739,22 @@ static int32_t q4_umma_forward(mpq_context* ctx, const Q4Dev& q, const float* x,
     Q4ULaunch p;
     p.stream = q.stream; p.XS = ctx->q4u_xs; p.inv_sc = inv_sc; p.Y = y; p.partial = ctx->q4_rect_partial;
     p.M = M; p.Mp = Mp; p.N = (int)q.N; p.ldy = ldy; p.nchunks = q.nchunks; p.nrp = q.nrp; p.ngroups = ng;
-    p.stack = stack;
-    p.T = bestT; p.nbatches = (ng + bestT - 1) / bestT; p.nks = nks; p.slice_chunks = slice; p.status = ctx->q4_status;
+    p.nbatches = nbatches; p.W = W; p.stack = stack; p.status = ctx->q4_status;
+    // shared memory: activation ring, the teams' weight rings as deep as the rest allows, barriers (+ 1 KiB for the alignment)
+    const size_t smem_max = (size_t)ctx->prop.sharedMemPerBlockOptin - 256, xring_bytes = (size_t)Q4U_XSTAGES * 2 * Mp * 128;
+    p.wstages = (int)std::min<size_t>(Q4U_MAX_WSTAGES, (smem_max - xring_bytes - 2048) / ((size_t)Q4U_TEAMS * Q4U_WSTAGE_BYTES));
+#ifdef MPQ_TRACE
+    p.trace = trace_buffer() ? g_trace + (size_t)(g_trace_n++ % 64) * 1024 * 16 : nullptr;
+#endif
     // at least 116 KiB, so that two CTAs never share an SM (each allocates all of its tensor memory)
-    const size_t smem = std::max<size_t>((size_t)Q4U_XSTAGES * 2 * Mp * 128 + (size_t)Q4U_WSTAGES * Q4U_WSTAGE_BYTES + 512 + 1024, (size_t)116 * 1024);
+    const size_t smem = std::max<size_t>(xring_bytes + (size_t)Q4U_TEAMS * p.wstages * Q4U_WSTAGE_BYTES + 1024 + 1024, (size_t)116 * 1024);
     static PerDeviceOnce configured;
     if (configured.needs(ctx->device)) {
-        CU_TRY(ctx, cudaFuncSetAttribute(q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024)));
+        CU_TRY(ctx, cudaFuncSetAttribute(q4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
         configured.mark(ctx->device);
     }
     cfg = {};
-    cfg.gridDim = dim3((unsigned)std::min(p.nbatches * p.nks, sms));
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(Q4U_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
@@ -743,16 +762,16 @@ static int32_t q4_umma_forward(mpq_context* ctx, const Q4Dev& q, const float* x,
     e = cudaLaunchKernelEx(&cfg, q4_umma_kernel, p);
     ctx->launches += 1;
     if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_umma_kernel launch failed: %s", cudaGetErrorString(e));
-    if (nks > 1) {
+    if (maxp > 1) {
         cfg = {};
-        const int64_t total = (int64_t)M * q.N;
-        cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)sms * 8));
+        const int64_t tot = (int64_t)M * ((q.N + 3) / 4);
+        cfg.gridDim = dim3((unsigned)std::min<int64_t>((tot + 255) / 256, (int64_t)sms * 8));
         cfg.blockDim = dim3(256);
         cfg.stream = s;
         launch_pdl(cfg, at, ctx->pdl);
-        e = cudaLaunchKernelEx(&cfg, q4_rect_reduce_kernel, (const float*)ctx->q4_rect_partial, nks, M, (int)q.N, y, ldy);
+        e = cudaLaunchKernelEx(&cfg, q4u_reduce_kernel, (const float*)ctx->q4_rect_partial, M, (int)q.N, q.nchunks, W, y, ldy);
         ctx->launches += 1;
-        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_rect_reduce_kernel launch failed: %s", cudaGetErrorString(e));
+        if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4u_reduce_kernel launch failed: %s", cudaGetErrorString(e));
     }
     return MPQ_OK;
 }
