@@ -152,6 +152,14 @@ __device__ __forceinline__ void q4u_bar_arrive(uint32_t bar)
 // bounded wait on a phase parity: false when the limit ran out.  try_wait with a suspend-time hint: without one a
 // failed try returns after a few dozen cycles, and the polling loops of the waiting warps were measured to issue as many
 // instructions as the expansion itself (the kernel is bound by instruction issue).
+// one non-suspending test of a phase parity (its round trip is about 200 cycles: tests of several barriers are issued together)
+__device__ __forceinline__ uint32_t q4u_bar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
 __device__ __forceinline__ bool q4u_bar_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
@@ -334,7 +342,9 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
             const uint32_t xph_now = xph;
             if (++xs == Q4U_XSTAGES) { xs = 0; xph ^= 1u; }
             Q4U_CYC(t_x)
-            if (!q4u_bar_wait(x_full + 8 * xs_now, xph_now)) { if (lane == 0) { atomicExch(p.status, 34); s_abort = 1; } break; }
+            const uint32_t okx = q4u_bar_test(x_full + 8 * xs_now, xph_now);
+            const uint32_t okf0 = q4u_bar_test(a_full + 16 * tm, (uint32_t)n & 1u);      // (only meaningful when this team's group exists)
+            if (!okx && !q4u_bar_wait(x_full + 8 * xs_now, xph_now)) { if (lane == 0) { atomicExch(p.status, 34); s_abort = 1; } break; }
             Q4U_CYC_ADD(cyc_x, t_x)
             if (b * Q4U_TEAMS + tm >= p.ngroups) {           // the last batch may lack groups: only the activation stage's hand-back
                 if (lane == 0) q4u_bar_arrive(x_empty + 8 * xs_now);
@@ -353,7 +363,7 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 Q4U_CYC(t_a)
-                if (!q4u_bar_wait(a_full + 16 * tm + 8 * hf, (uint32_t)n & 1u)) { if (lane == 0) { atomicExch(p.status, 35); s_abort = 1; } live = false; break; }
+                if (!(hf == 0 && okf0) && !q4u_bar_wait(a_full + 16 * tm + 8 * hf, (uint32_t)n & 1u)) { if (lane == 0) { atomicExch(p.status, 35); s_abort = 1; } live = false; break; }
                 Q4U_CYC_ADD(cyc_a, t_a)
                 q4u_fence_after();
                 Q4U_CYC(t_i)
@@ -409,6 +419,7 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
         int n = 0, drains = 0, seg_n = 0, wsi = 0;
         uint32_t wph = 0;
         bool waited = false, live = true;
+        float isc0 = 0.f, isc1 = 0.f;
 #ifdef MPQ_TRACE
         long long cyc_w = 0, cyc_ae = 0, cyc_df = 0, cyc_exp = 0, cyc_st = 0, cyc_drain = 0, cyc_store = 0, gap_top = 0, gap_lds = 0, gap_arr = 0, t_prev = 0;
         const long long cyc_t0 = clock64();
@@ -426,7 +437,10 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
             if (t_prev) gap_top += clock64() - t_prev;
 #endif
             Q4U_CYC(t_w)
-            if (!q4u_bar_wait(w_full + 8 * ws, wph_now)) { if (lane == 0) { atomicExch(p.status, 36); s_abort = 1; } break; }
+            // the stage's three waits usually find their phases complete: their tests go out together (one round trip)
+            const uint32_t okw = q4u_bar_test(w_full + 8 * ws, wph_now);
+            const uint32_t oka[2] = {q4u_bar_test(a_empty + 16 * tm, ((uint32_t)n & 1u) ^ 1u), q4u_bar_test(a_empty + 16 * tm + 8, ((uint32_t)n & 1u) ^ 1u)};
+            if (!okw && !q4u_bar_wait(w_full + 8 * ws, wph_now)) { if (lane == 0) { atomicExch(p.status, 36); s_abort = 1; } break; }
             Q4U_CYC_ADD(cyc_w, t_w)
             Q4U_CYC(t_g1)
             const uint32_t base = wring + ws * Q4U_WSTAGE_BYTES;
@@ -446,7 +460,7 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 Q4U_CYC(t_ae)
-                if (!q4u_bar_wait(a_empty + 16 * tm + 8 * hf, ((uint32_t)n & 1u) ^ 1u)) { if (lane == 0) { atomicExch(p.status, 37); s_abort = 1; } live = false; break; }
+                if (!oka[hf] && !q4u_bar_wait(a_empty + 16 * tm + 8 * hf, ((uint32_t)n & 1u) ^ 1u)) { if (lane == 0) { atomicExch(p.status, 37); s_abort = 1; } live = false; break; }
                 Q4U_CYC_ADD(cyc_ae, t_ae)
                 q4u_fence_after();
                 Q4U_CYC(t_e)
@@ -550,7 +564,14 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
             if (!piece_last) continue;
             Q4U_CYC(t_so)
             // ---- the piece's sums: to y when this range holds the whole batch, else to the piece's slice
-            if (!waited) { asm volatile("griddepcontrol.wait;" ::: "memory"); waited = true; }    // inv_sc comes from the kernel before this one
+            // inv_sc comes from the kernel before this one.  Lane l keeps rows l and l + 32 of it: read inside the store loop
+            // the loads would be ordered behind the stores (they may alias for all the compiler knows), one round trip per row.
+            if (!waited) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                waited = true;
+                isc0 = lane < p.M ? p.inv_sc[lane] : 0.f;
+                isc1 = lane + 32 < p.M ? p.inv_sc[lane + 32] : 0.f;
+            }
             int pf, pl;
             q4u_pieces(b, p.nchunks, p.W, &pf, &pl);
             const int nrow = g * 128 + qd * 32 + lane;
@@ -558,7 +579,8 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
             const int64_t ld = pf == pl ? p.ldy : (int64_t)p.N;
 #pragma unroll
             for (int m = 0; m < 64; ++m) {
-                if (m < p.M && nrow < p.N) out[(size_t)m * ld + nrow] = racc[m] * p.inv_sc[m];
+                const float sc = __shfl_sync(0xFFFFFFFFu, m < 32 ? isc0 : isc1, m & 31);
+                if (m < p.M && nrow < p.N) out[(size_t)m * ld + nrow] = racc[m] * sc;
                 racc[m] = 0.f;
             }
             Q4U_CYC_ADD(cyc_store, t_so)

@@ -264,8 +264,9 @@ def test_rectangle_kernel_covers_every_row_count(orc):
 
 
 def test_tcgen05_kernel_covers_every_row_count(orc):
-    """The tcgen05 kernel (by default used from 33 activation rows up) forced on from 5 rows: every accumulator width, both
-    MMA forms (one or two MMAs for the hi part), one and several K ranges, several K segments, ragged last groups; outputs
+    """The tcgen05 kernel (by default used from 17 activation rows up) forced on from 5 rows: every accumulator width, both
+    MMA forms (one or two MMAs for the hi part), batches kept whole and cut into pieces, several K segments, ragged last groups
+    and batches; outputs
     beyond the matrix stay untouched and two runs give the same bits."""
     import makepad_b200
     torch = _torch()
