@@ -189,6 +189,16 @@ int32_t mpq_exchange_destroy(mpq_exchange* ex);
 int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, mpq_exchange* ex,
                                         const float* x_dev, int64_t M, float* y_dev, void* stream);
 
+/* ---- SwiGLU between the gate+up and the down projection ------------------- */
+/* out[M][F] = silu(gate) * up for gate_up[M][2F] = [gate | up], fp32: silu(g) = g / (1 + exp(-g)) with a
+ * correctly rounded division.  F must be a multiple of 4; 16-byte aligned pointers. */
+int32_t mpq_swiglu(mpq_context* ctx, const float* gate_up_dev, int64_t M, int64_t F, float* out_dev, void* stream);
+/* Y[M][N] = swiglu(gate_up)[M][K] * W^T with gate_up[M][2K]: the down projection with the SwiGLU fused into
+ * the kernel's activation staging (M <= 4: the intermediate never exists in memory; larger M run
+ * mpq_swiglu into scratch the context owns, then mpq_q4_linear_forward).  Same bits as the two calls. */
+int32_t mpq_q4_linear_forward_swiglu(mpq_context* ctx, const mpq_weight* w, const float* gate_up_dev, int64_t M,
+                                     float* y_dev, void* stream);
+
 /* ---- NVFP4 GEMM ---------------------------------------------------------- */
 /* C[M][N] (bf16 bits, row-major) = bf16( tsA * tsB * sum_k A~[m,k] * B~[n,k] ).
  * A is canonical NVFP4 on the device: codes [M][K/2], sf [M][K/16]; any
@@ -207,6 +217,11 @@ int32_t mpq_nvfp4_gemm_forward(mpq_context* ctx, const mpq_weight* w,
  * be a multiple of 16; non-finite inputs are not supported. */
 int32_t mpq_nvfp4_quantize_activations(mpq_context* ctx, const void* x_dev, int32_t x_is_bf16, int64_t M, int64_t K,
                                        float tensor_scale, uint8_t* codes_dev, uint8_t* sf_dev, void* stream);
+/* The same with SwiGLU fused in front: gate_up[M][2F] = [gate | up] (fp32, or bf16 bits) -> NVFP4 of
+ * h = silu(gate) * up (computed in fp32 exactly as mpq_swiglu does; h itself is never written to memory).
+ * F must be a multiple of 16.  No counterpart in the reference. */
+int32_t mpq_nvfp4_quantize_swiglu(mpq_context* ctx, const void* gate_up_dev, int32_t x_is_bf16, int64_t M, int64_t F,
+                                  float tensor_scale, uint8_t* codes_dev, uint8_t* sf_dev, void* stream);
 /* Exact fp32 export [R][K] of a canonical NVFP4 tensor on the device. */
 int32_t mpq_nvfp4_dequantize(mpq_context* ctx, int64_t R, int64_t K, const uint8_t* codes_dev,
                              const uint8_t* sf_dev, float tensor_scale, float* out_dev, void* stream);

@@ -65,6 +65,9 @@ SIGNATURES = {
     "mpq_nvfp4_gemm_forward": (_i32, [_vp, _vp, _vp, _vp, _f32, _i64, _vp, _vp]),
     "mpq_nvfp4_dequantize": (_i32, [_vp, _i64, _i64, _vp, _vp, _f32, _vp, _vp]),
     "mpq_nvfp4_quantize_activations": (_i32, [_vp, _vp, _i32, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "mpq_nvfp4_quantize_swiglu": (_i32, [_vp, _vp, _i32, _i64, _i64, _f32, _vp, _vp, _vp]),
+    "mpq_swiglu": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "mpq_q4_linear_forward_swiglu": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp]),
     "mpq_file_info": (_i32, [C.c_char_p, C.POINTER(FileInfo)]),
     "mpq_canonical_save": (_i32, [C.c_char_p, _i32, _i64, _i64, _vp, _vp, _f32]),
     "mpq_canonical_load": (_i32, [C.c_char_p, _vp, _i64, _vp, _i64, C.POINTER(_f32)]),

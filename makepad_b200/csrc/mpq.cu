@@ -38,6 +38,8 @@ struct mpq_context {
     // between two CTAs' runs (two slots per CTA; write-once / read-once per launch), one status word
     unsigned char* q4u_xs;    // staged activations of the tcgen05 kernel (grown on demand), then 64 floats of row scales
     size_t q4u_xs_bytes;
+    float* swiglu_buf;        // SwiGLU output for the Q4 kernels that do not fuse it (grown on demand)
+    size_t swiglu_bytes;
     int q4_umma_min;          // fewest activation rows routed to the tcgen05 kernel (0 = never)
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
@@ -140,6 +142,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_partials = nullptr;
     c->q4u_xs = nullptr;
     c->q4u_xs_bytes = 0;
+    c->swiglu_buf = nullptr;
+    c->swiglu_bytes = 0;
     c->q4_rect_partial = nullptr;
     c->q4_rect_partial_bytes = 0;
     c->q4_partials_ctas = 0;
@@ -186,6 +190,7 @@ extern "C" int32_t mpq_context_destroy(mpq_context* ctx)
     cudaFree(ctx->hy);
     cudaFree(ctx->q4_partials);
     cudaFree(ctx->q4u_xs);
+    cudaFree(ctx->swiglu_buf);
     cudaFree(ctx->q4_rect_partial);
     cudaFree(ctx->q4_status);
     ctx->fp4.release();
@@ -482,6 +487,7 @@ static int q4_stream_params(const mpq_context* ctx, const Q4Dev& q, const Q4Stre
     p->tile_mode = (ctx->q4_tile_mode && (int64_t)q.nrp * 10 >= (int64_t)sms * 6) ? 1 : 0;
     p->nrp = q.nrp;
     p->stream = q.stream; p->X = x; p->Y = y; p->M = M; p->N = (int)q.N; p->K = (int)q.K; p->ldy = ldy;
+    p->swiglu = 0;
     p->nchunks = q.nchunks; p->groups = groups; p->warps_total = W; p->depth = pl.depth; p->pre = pl.pre;
     p->partials = nullptr; p->status = nullptr;
     p->xworld = 0; p->xrank = 0; p->xslot = 0; p->xlimit = 0;
@@ -872,6 +878,79 @@ extern "C" int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, 
     return q4_forward_checked(ctx, w, x_dev, M, y_dev, w->q4.N, (cudaStream_t)stream);
 }
 
+// out[M][F] from gu[M][2F]; F a multiple of 4, 16-byte aligned pointers
+__global__ void __launch_bounds__(256) swiglu_kernel(const float* __restrict__ gu, int64_t M, int64_t F, float* __restrict__ out)
+{
+    const int64_t f4 = F / 4, total = M * f4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / f4, f = (i - m * f4) * 4;
+        const float4 g = *reinterpret_cast<const float4*>(gu + m * 2 * F + f);
+        const float4 u = *reinterpret_cast<const float4*>(gu + m * 2 * F + F + f);
+        *reinterpret_cast<float4*>(out + m * F + f) = swiglu_f32x4(g, u);
+    }
+}
+
+
+static int32_t swiglu_check(mpq_context* ctx, const void* gate_up, int64_t M, int64_t F, const void* out)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!gate_up || !out) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    if (M <= 0 || M > (1 << 20) || F <= 0 || F % 4) return fail(ctx, MPQ_ERR_SHAPE, "SwiGLU needs 0 < M <= 2^20 and F a positive multiple of 4");
+    if (!aligned16(gate_up) || !aligned16(out)) return fail(ctx, MPQ_ERR_ALIGN, "gate_up and out must be 16-byte aligned");
+    return MPQ_OK;
+}
+
+static int32_t swiglu_launch(mpq_context* ctx, const float* gate_up, int64_t M, int64_t F, float* out, cudaStream_t s)
+{
+    const int64_t total = M * (F / 4);
+    const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->prop.multiProcessorCount * 16);
+    swiglu_kernel<<<grid, 256, 0, s>>>(gate_up, M, F, out);
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_swiglu(mpq_context* ctx, const float* gate_up_dev, int64_t M, int64_t F, float* out_dev, void* stream)
+{
+    int32_t st = swiglu_check(ctx, gate_up_dev, M, F, out_dev);
+    if (st) return st;
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    return swiglu_launch(ctx, gate_up_dev, M, F, out_dev, (cudaStream_t)stream);
+}
+
+// y = W * swiglu(gate_up): fused into the streaming kernel's activation staging for M <= 4 (the intermediate never
+// exists in memory); above that the SwiGLU runs as its own kernel into scratch the context owns.
+extern "C" int32_t mpq_q4_linear_forward_swiglu(mpq_context* ctx, const mpq_weight* w, const float* gate_up_dev, int64_t M,
+                                                float* y_dev, void* stream)
+{
+    int32_t st = q4_validate(ctx, w, gate_up_dev, M, y_dev);
+    if (st) return st;
+    if (!aligned16(gate_up_dev) || !aligned16(y_dev)) return fail(ctx, MPQ_ERR_ALIGN, "gate_up and y must be 16-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    const Q4Dev& q = w->q4;
+    cudaStream_t s = (cudaStream_t)stream;
+    Q4StreamPlan pl;
+    if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) {
+        Q4StreamLaunch p;
+        const int grid = q4_stream_params(ctx, q, pl, gate_up_dev, (int)M, y_dev, q.N, &p);
+        if ((st = q4_stream_scratch(ctx, grid))) return st;
+        p.partials = ctx->q4_partials; p.status = ctx->q4_status;
+        p.swiglu = 1;
+        return q4_stream_enqueue(ctx, pl, p, grid, s);
+    }
+    const size_t need = (size_t)M * q.K * sizeof(float);
+    if (ctx->swiglu_bytes < need) {
+        CU_TRY(ctx, cudaDeviceSynchronize());
+        cudaFree(ctx->swiglu_buf);
+        ctx->swiglu_buf = nullptr;
+        ctx->swiglu_bytes = 0;
+        CU_TRY(ctx, cudaMalloc(&ctx->swiglu_buf, need));
+        ctx->swiglu_bytes = need;
+    }
+    if ((st = swiglu_launch(ctx, gate_up_dev, M, q.K, ctx->swiglu_buf, s))) return st;
+    return q4_forward_checked(ctx, w, ctx->swiglu_buf, M, y_dev, q.N, s);
+}
+
 static int32_t grow(mpq_context* ctx, float** buf, size_t* have, size_t need)
 {
     if (*have >= need) return MPQ_OK;
@@ -1214,7 +1293,22 @@ extern "C" int32_t mpq_nvfp4_quantize_activations(mpq_context* ctx, const void* 
     if (!(tensor_scale > 0.f)) return fail(ctx, MPQ_ERR_INVALID_ARG, "tensor_scale must be positive");
     if (!aligned16(x_dev) || (reinterpret_cast<uintptr_t>(codes_dev) & 7u)) return fail(ctx, MPQ_ERR_ALIGN, "x must be 16-byte, codes 8-byte aligned");
     CU_TRY(ctx, cudaSetDevice(ctx->device));
-    nvfp4_quantize_launch(x_dev, x_is_bf16 != 0, M, K, tensor_scale, codes_dev, sf_dev, (cudaStream_t)stream);
+    nvfp4_quantize_launch(x_dev, x_is_bf16 != 0, false, M, K, tensor_scale, codes_dev, sf_dev, (cudaStream_t)stream);
+    ctx->launches += 1;
+    CU_TRY(ctx, cudaGetLastError());
+    return MPQ_OK;
+}
+
+extern "C" int32_t mpq_nvfp4_quantize_swiglu(mpq_context* ctx, const void* gate_up_dev, int32_t x_is_bf16, int64_t M, int64_t F,
+                                             float tensor_scale, uint8_t* codes_dev, uint8_t* sf_dev, void* stream)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!gate_up_dev || !codes_dev || !sf_dev) return fail(ctx, MPQ_ERR_INVALID_ARG, "null pointer");
+    if (M <= 0 || F <= 0 || F % 16) return fail(ctx, MPQ_ERR_SHAPE, "NVFP4 needs M > 0 and F a positive multiple of 16");
+    if (!(tensor_scale > 0.f)) return fail(ctx, MPQ_ERR_INVALID_ARG, "tensor_scale must be positive");
+    if (!aligned16(gate_up_dev) || (reinterpret_cast<uintptr_t>(codes_dev) & 7u)) return fail(ctx, MPQ_ERR_ALIGN, "gate_up must be 16-byte, codes 8-byte aligned");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    nvfp4_quantize_launch(gate_up_dev, x_is_bf16 != 0, true, M, F, tensor_scale, codes_dev, sf_dev, (cudaStream_t)stream);
     ctx->launches += 1;
     CU_TRY(ctx, cudaGetLastError());
     return MPQ_OK;

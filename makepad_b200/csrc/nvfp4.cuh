@@ -38,7 +38,7 @@ void nvfp4_dequant_launch(const uint8_t* codes, const uint8_t* sf, float ts, int
 int32_t nvfp4_weight_build(Nvfp4Dev& w, int64_t N, int64_t K, const uint8_t* codes_host, const uint8_t* sf_host, float ts,
                            int* launches, std::string& err);
 // fp32 (or bf16) rows -> canonical NVFP4 codes [R][K/2] and e4m3 scales [R][K/16]
-void nvfp4_quantize_launch(const void* x, bool bf16, int64_t R, int64_t K, float ts, uint8_t* codes, uint8_t* sf, cudaStream_t s);
+void nvfp4_quantize_launch(const void* x, bool bf16, bool swiglu, int64_t R, int64_t K, float ts, uint8_t* codes, uint8_t* sf, cudaStream_t s);
 // bytes of a weight's tiled scale factors in the current layout
 size_t nvfp4_sf_tiled_bytes(int64_t N, int64_t K);
 // exact fp32 export [N][K] of a weight, its scale factors read back from the tiled device layout

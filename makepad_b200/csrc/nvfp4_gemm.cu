@@ -32,6 +32,7 @@
 #include <cstdlib>
 
 #include "nvfp4.cuh"
+#include "swiglu.cuh"
 #include "per_device.h"
 
 namespace mpq {
@@ -116,15 +117,12 @@ __device__ __forceinline__ uint32_t f32_to_e2m1_sat(float f)
     return sign | m;
 }
 
+// 16 consecutive elements starting at element `at` of a row-major fp32 or bf16 array
 template <bool BF16>
-__global__ void nvfp4_quantize_kernel(const void* __restrict__ xin, int64_t R, int64_t K, float ts, uint8_t* __restrict__ codes,
-                                      uint8_t* __restrict__ sf)
+__device__ __forceinline__ void nvfp4_load16(const void* xin, int64_t at, float (&v)[16])
 {
-    const int64_t blk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (blk >= R * (K / 16)) return;
-    float v[16];
     if (BF16) {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(xin) + blk * 16);
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(xin) + at);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
             const uint4 u = src[q];
@@ -136,12 +134,32 @@ __global__ void nvfp4_quantize_kernel(const void* __restrict__ xin, int64_t R, i
             }
         }
     } else {
-        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(xin) + blk * 16);
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(xin) + at);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const float4 f = src[q];
             v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
         }
+    }
+}
+
+// SWIGLU: the input is [R][2K] = [gate | up] and what is quantised is silu(gate) * up (fp32), never written to memory.
+template <bool BF16, bool SWIGLU>
+__global__ void nvfp4_quantize_kernel(const void* __restrict__ xin, int64_t R, int64_t K, float ts, uint8_t* __restrict__ codes,
+                                      uint8_t* __restrict__ sf)
+{
+    const int64_t blk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (blk >= R * (K / 16)) return;
+    float v[16];
+    if (SWIGLU) {
+        const int64_t r = blk / (K / 16), k0 = (blk - r * (K / 16)) * 16;
+        float u[16];
+        nvfp4_load16<BF16>(xin, r * 2 * K + k0, v);
+        nvfp4_load16<BF16>(xin, r * 2 * K + K + k0, u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = swiglu_f32(v[i], u[i]);
+    } else {
+        nvfp4_load16<BF16>(xin, blk * 16, v);
     }
     float amax = 0.f;
 #pragma unroll
@@ -160,12 +178,17 @@ __global__ void nvfp4_quantize_kernel(const void* __restrict__ xin, int64_t R, i
     sf[blk] = (uint8_t)s8;
 }
 
-void nvfp4_quantize_launch(const void* x, bool bf16, int64_t R, int64_t K, float ts, uint8_t* codes, uint8_t* sf, cudaStream_t s)
+void nvfp4_quantize_launch(const void* x, bool bf16, bool swiglu, int64_t R, int64_t K, float ts, uint8_t* codes, uint8_t* sf, cudaStream_t s)
 {
     const int64_t blocks = R * (K / 16);
     const unsigned grid = (unsigned)((blocks + 255) / 256);
-    if (bf16) nvfp4_quantize_kernel<true><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
-    else nvfp4_quantize_kernel<false><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+    if (swiglu) {
+        if (bf16) nvfp4_quantize_kernel<true, true><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+        else nvfp4_quantize_kernel<false, true><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+    } else {
+        if (bf16) nvfp4_quantize_kernel<true, false><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+        else nvfp4_quantize_kernel<false, false><<<grid, 256, 0, s>>>(x, R, K, ts, codes, sf);
+    }
 }
 
 // ---------------------------------------------------------------------------

@@ -31,6 +31,7 @@
 // 32-block accumulates in fp32; the block's fp16 scale multiplies the pair's
 // result in fp32.  Padded rows / K carry code 0 and scale 0.
 #pragma once
+#include "swiglu.cuh"
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -459,9 +460,10 @@ constexpr size_t Q4S_SLOT_BYTES_PER_CTA = 2 * 32 * 4 * sizeof(uint2);   // two t
 
 struct Q4StreamLaunch {
     const uint4* stream;
-    const float* X;         // [M][K]
+    const float* X;         // [M][K]; with swiglu: [M][2K] = [gate | up], and the activation is silu(gate) * up
     float* Y;               // [M][ldy]
     int M, N, K;
+    int swiglu;             // 1: SwiGLU is applied while the activation is staged
     int64_t ldy;
     int nchunks;            // per row pair-tile, a multiple of G
     int groups;             // nrp * nchunks / G
@@ -731,7 +733,14 @@ __device__ __forceinline__ uint32_t q4s_stage_pass(const Q4StreamLaunch& p, int 
             mm[u] = (ii >= pk4) + (ii >= 2 * pk4) + (ii >= 3 * pk4);       // M <= 4
             ff[u] = ii - mm[u] * pk4;
             v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (on[u] && 4 * ff[u] < p.K) v[u] = *reinterpret_cast<const float4*>(p.X + (size_t)mm[u] * p.K + 4 * ff[u]);
+            if (on[u] && 4 * ff[u] < p.K) {
+                if (p.swiglu) {
+                    const float* row = p.X + (size_t)mm[u] * 2 * p.K + 4 * ff[u];
+                    v[u] = swiglu_f32x4(*reinterpret_cast<const float4*>(row), *reinterpret_cast<const float4*>(row + p.K));
+                } else {
+                    v[u] = *reinterpret_cast<const float4*>(p.X + (size_t)mm[u] * p.K + 4 * ff[u]);
+                }
+            }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {

@@ -210,3 +210,42 @@ class QuantLinear:
         return y
 
     __call__ = forward
+
+    def forward_swiglu(self, gate_up, out=None):
+        """Q4 only: y = (silu(gate) * up) . W^T for gate_up fp32 [M][2K] = [gate | up] on the GPU (the down projection of a
+        feed-forward block with the SwiGLU fused into the kernel's activation staging)."""
+        import torch
+        w, ctx = self.w, self.ctx
+        if w.fmt != _lib.FMT_Q4:
+            raise MpqError(_lib.ERR_INVALID_ARG, "forward_swiglu is for Q4 weights")
+        if gate_up.dtype != torch.float32 or not gate_up.is_cuda or not gate_up.is_contiguous():
+            raise MpqError(_lib.ERR_INVALID_ARG, "gate_up must be a contiguous fp32 CUDA tensor")
+        g2 = gate_up.reshape(-1, 2 * w.K)
+        y = torch.empty((g2.shape[0], w.N), dtype=torch.float32, device=gate_up.device) if out is None else out
+        ctx.check(ctx.lib.mpq_q4_linear_forward_swiglu(ctx.h, w.h, C.c_void_p(g2.data_ptr()), g2.shape[0], C.c_void_p(y.data_ptr()),
+                                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return y
+
+
+def swiglu(ctx: Context, gate_up):
+    """silu(gate) * up for gate_up fp32 [M][2F] = [gate | up] on the GPU -> fp32 [M][F]."""
+    import torch
+    M, F2 = gate_up.shape
+    out = torch.empty((M, F2 // 2), dtype=torch.float32, device=gate_up.device)
+    ctx.check(ctx.lib.mpq_swiglu(ctx.h, C.c_void_p(gate_up.data_ptr()), M, F2 // 2, C.c_void_p(out.data_ptr()),
+                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out
+
+
+def nvfp4_quantize(ctx: Context, x, tensor_scale: float = 1.0, swiglu_fused: bool = False):
+    """fp32 or bf16 [M][K] on the GPU -> (codes u8 [M][K/2], sf u8 [M][K/16]) ready to be the GEMM's A.  With swiglu_fused
+    the input is [M][2K] = [gate | up] and silu(gate) * up is what gets quantised."""
+    import torch
+    M = x.shape[0]
+    K = x.shape[1] // 2 if swiglu_fused else x.shape[1]
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((M, K // 16), dtype=torch.uint8, device=x.device)
+    fn = ctx.lib.mpq_nvfp4_quantize_swiglu if swiglu_fused else ctx.lib.mpq_nvfp4_quantize_activations
+    ctx.check(fn(ctx.h, C.c_void_p(x.data_ptr()), 1 if x.dtype == torch.bfloat16 else 0, M, K, C.c_float(tensor_scale),
+                 C.c_void_p(codes.data_ptr()), C.c_void_p(sf.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return codes, sf

@@ -158,6 +158,16 @@ def nvfp4_quantize(x, tscale=1.0):
     return codes, sf
 
 
+def swiglu_f64(gate_up):
+    """[M][2F] = [gate | up] -> silu(gate) * up in binary64, silu(g) = g / (1 + exp(-g)): the reference the GPU's fp32
+    SwiGLU is held against (a transcendental: checked to a tolerance, not to the bit)."""
+    gu = np.asarray(gate_up, dtype=np.float64)
+    F = gu.shape[1] // 2
+    g, u = gu[:, :F], gu[:, F:]
+    with np.errstate(over="ignore"):
+        return g / (1.0 + np.exp(-g)) * u
+
+
 def nvfp4_gemm(a, sfa, ta, b, sfb, tb, threads=0):
     """Returns (C fp32 [M,N], C bf16 bits [M,N]); B is stored [N][K/2]."""
     M, K = a.shape[0], a.shape[1] * 2
