@@ -97,6 +97,9 @@ pub struct LibMpq {
     pub mpq_nvfp4_gemm_forward: unsafe extern "C" fn(*mut mpq_context, *const mpq_weight, *const u8, *const u8, f32, i64, *mut u16, *mut c_void) -> i32,
     pub mpq_nvfp4_dequantize: unsafe extern "C" fn(*mut mpq_context, i64, i64, *const u8, *const u8, f32, *mut f32, *mut c_void) -> i32,
     pub mpq_nvfp4_quantize_activations: unsafe extern "C" fn(*mut mpq_context, *const c_void, i32, i64, i64, f32, *mut u8, *mut u8, *mut c_void) -> i32,
+    pub mpq_nvfp4_quantize_swiglu: unsafe extern "C" fn(*mut mpq_context, *const c_void, i32, i64, i64, f32, *mut u8, *mut u8, *mut c_void) -> i32,
+    pub mpq_swiglu: unsafe extern "C" fn(*mut mpq_context, *const f32, i64, i64, *mut f32, *mut c_void) -> i32,
+    pub mpq_q4_linear_forward_swiglu: unsafe extern "C" fn(*mut mpq_context, *const mpq_weight, *const f32, i64, *mut f32, *mut c_void) -> i32,
     pub mpq_file_info: unsafe extern "C" fn(*const c_char, *mut mpq_file_info_t) -> i32,
     pub mpq_canonical_save: unsafe extern "C" fn(*const c_char, i32, i64, i64, *const u8, *const c_void, f32) -> i32,
     pub mpq_canonical_load: unsafe extern "C" fn(*const c_char, *mut u8, i64, *mut c_void, i64, *mut f32) -> i32,
@@ -158,6 +161,9 @@ impl LibMpq {
                 mpq_nvfp4_gemm_forward: sym!(h, "mpq_nvfp4_gemm_forward"),
                 mpq_nvfp4_dequantize: sym!(h, "mpq_nvfp4_dequantize"),
                 mpq_nvfp4_quantize_activations: sym!(h, "mpq_nvfp4_quantize_activations"),
+                mpq_nvfp4_quantize_swiglu: sym!(h, "mpq_nvfp4_quantize_swiglu"),
+                mpq_swiglu: sym!(h, "mpq_swiglu"),
+                mpq_q4_linear_forward_swiglu: sym!(h, "mpq_q4_linear_forward_swiglu"),
                 mpq_file_info: sym!(h, "mpq_file_info"),
                 mpq_canonical_save: sym!(h, "mpq_canonical_save"),
                 mpq_canonical_load: sym!(h, "mpq_canonical_load"),
