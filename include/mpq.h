@@ -118,11 +118,15 @@ int32_t mpq_weight_destroy(mpq_weight* w);
 /* Forward calls on one context share that context's scratch buffers: issue
  * them in stream order (one stream per context at a time).
  * Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
- * row-major device arrays, 16-byte aligned.  Any M >= 1 (M <= 4 is one
- * launch of the streaming kernel; larger M runs as several launches over
- * slabs of rows).  Finite inputs with |x| < 3e38 are handled at any magnitude
- * (each CTA renormalises its slice by a power of two); a non-finite x yields
- * non-finite outputs in its row. */
+ * row-major device arrays, 16-byte aligned.  Any M >= 1: M <= 4 is one
+ * launch of the streaming kernel; 5..16 rows one pass of the rectangle kernel
+ * (weights read once) plus a small reduction; from 17 rows slabs of up to 64
+ * rows through the tcgen05 kernel (activation staging, main kernel, reduction
+ * of the pieces).  The first call that needs a scratch buffer (or a larger
+ * one) allocates it: make a warm-up call with the largest M before capturing
+ * a CUDA graph.  Finite inputs with |x| < 3e38 are handled at any magnitude
+ * (rows are renormalised by a power of two); a non-finite x yields non-finite
+ * outputs in its row. */
 int32_t mpq_q4_linear_forward(mpq_context* ctx, const mpq_weight* w, const float* x_dev, int64_t M,
                               float* y_dev, void* stream);
 /* Same result as mpq_q4_linear_forward for callers that must not let the
