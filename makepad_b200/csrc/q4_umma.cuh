@@ -51,8 +51,7 @@ constexpr int Q4U_WSTAGE_BYTES = 4 * Q4_UNIT_BYTES;
 constexpr int Q4U_XSTAGES = 4;                // activation ring: stages of one chunk (hi tile + lo tile)
 constexpr int Q4U_SEG = 16;                   // chunks (1024 of K) a team accumulates inside the tensor core before its sums are drained
 constexpr int Q4U_A_COL = 256;                // accumulators: columns [0, 256), 64 per team; A stages: [256, 512), 64 per team
-constexpr uint32_t Q4U_SUSPEND_NS = 2000;     // how long one try_wait may suspend the thread
-constexpr uint32_t Q4U_SPIN = 1u << 20;       // tries of one mbarrier before giving up (about two seconds)
+constexpr uint32_t Q4U_SPIN = 1u << 22;       // tries of one mbarrier before giving up
 
 struct Q4ULaunch {
     const uint4* stream;          // the Q4 tile stream
@@ -149,9 +148,6 @@ __device__ __forceinline__ void q4u_bar_arrive(uint32_t bar)
 {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// bounded wait on a phase parity: false when the limit ran out.  try_wait with a suspend-time hint: without one a
-// failed try returns after a few dozen cycles, and the polling loops of the waiting warps were measured to issue as many
-// instructions as the expansion itself (the kernel is bound by instruction issue).
 // one non-suspending test of a phase parity (its round trip is about 200 cycles: tests of several barriers are issued together)
 __device__ __forceinline__ uint32_t q4u_bar_test(uint32_t bar, uint32_t parity)
 {
@@ -160,16 +156,17 @@ __device__ __forceinline__ uint32_t q4u_bar_test(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// bounded wait on a phase parity: false when the limit ran out.  One non-suspending test first (most waits find their
+// phase complete), then try_wait, which suspends the thread for a hardware-chosen time per try.  (A suspend-time hint made
+// the compiler emit a nanosleep polling loop with more instructions; spinning on test_wait issues more still; none of
+// the three forms changed the kernel's time.)
 __device__ __forceinline__ bool q4u_bar_wait(uint32_t bar, uint32_t parity)
 {
-    uint32_t ok;
-    // most waits find their phase complete: one non-suspending test first
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
+    if (q4u_bar_test(bar, parity)) return true;
     for (uint32_t n = 0; n < Q4U_SPIN; ++n) {
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(Q4U_SUSPEND_NS) : "memory");
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
     }
     return false;
@@ -410,7 +407,7 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
         const uint32_t code_off = (uint32_t)qd * Q4_UNIT_BYTES + tile * 512 + g8 * 64;
         const uint32_t scale_off = (uint32_t)qd * Q4_UNIT_BYTES + 1024 + g8 * 16 + tile * 8 + h * 4;
         const uint32_t shA = 4 * h, shB = 4 * h + 8;
-        const __half2 k1032 = __floats2half2_rn(1032.f, 1032.f);
+        const uint32_t k1032 = 0x64086408u;                             // fp16 1032, twice
         const uint32_t dst = tmem + lanes + Q4U_A_COL + (uint32_t)tm * 64;
         const uint32_t dacc = tmem + lanes + (uint32_t)tm * 64;
         float racc[64];                                                 // running fp32 sums of the drained segments, one per activation row (local memory: touched once per segment)
@@ -466,7 +463,6 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
                 Q4U_CYC(t_e)
                 const uint32_t s16 = hf == 0 ? (sw & 0xFFFFu) : (sw >> 16);
                 const uint32_t s2u = s16 | (s16 << 16);
-                const __half2 s2 = *reinterpret_cast<const __half2*>(&s2u);
 #pragma unroll
                 for (int jj = 0; jj < 2; ++jj) {
                     const int j = 2 * hf + jj;
@@ -477,11 +473,12 @@ __global__ void __launch_bounds__(Q4U_THREADS, 1) q4_umma_kernel(const __grid_co
 #pragma unroll
                         for (int u = 0; u < 2; ++u) {            // k = 16j + 2t (+8): tensor-memory column t (+4) of the step
                             const uint32_t bits = ((w >> (u ? shB : shA)) & 0x000F000Fu) | 0x64006400u;      // halves 1024 + n
-                            const __half2 code = __hsub2(*reinterpret_cast<const __half2*>(&bits), k1032);  // n - 8, exact
-                            const __half2 vh = __hmul2(code, s2);
-                            const __half2 vl = __hfma2(code, s2, __hneg2(vh));                              // exact remainder
-                            hi[t + 4 * u] = *reinterpret_cast<const uint32_t*>(&vh);
-                            lo[t + 4 * u] = *reinterpret_cast<const uint32_t*>(&vl);
+                            uint32_t code, vh, vl;                                                             // fp16 pairs in plain registers
+                            asm("sub.f16x2 %0, %1, %2;" : "=r"(code) : "r"(bits), "r"(k1032));                // n - 8, exact
+                            asm("mul.f16x2 %0, %1, %2;" : "=r"(vh) : "r"(code), "r"(s2u));
+                            asm("{\n\t.reg .b32 t;\n\tneg.f16x2 t, %3;\n\tfma.rn.f16x2 %0, %1, %2, t;\n\t}" : "=r"(vl) : "r"(code), "r"(s2u), "r"(vh));   // exact remainder
+                            hi[t + 4 * u] = vh;
+                            lo[t + 4 * u] = vl;
                         }
                     }
                     q4u_st8(dst + hf * 32 + jj * 8, hi);
