@@ -185,6 +185,15 @@ def ceilings(ctx):
         ts.append(e0.elapsed_time(e1))
     out["fp4_mma_only_tflops"] = flop.value / (min(ts) * 1e-3) / 1e12
     out["fp4_mma_only_note"] = f"{mmas} tcgen05.mma kind::mxf4nvf4 128x224x64 per SM, operands resident, best of 5"
+    # issue rate of small fp16 MMAs (what the Q4 tcgen05 kernel is built around): SM cycles per MMA of 128 x n x 16
+    cyc = C.c_double()
+    issue = {}
+    for n_cols in (32, 64):
+        for issuers in (1, 2, 4):
+            ctx.check(ctx.lib.mpq_probe_f16_mma(ctx.h, n_cols, issuers, 4096, C.byref(cyc)))
+            issue[f"n{n_cols}_issuers{issuers}"] = round(cyc.value, 1)
+    out["f16_mma_cycles_per_mma"] = issue
+    out["f16_mma_note"] = "tcgen05.mma kind::f16 128 x n x 16, A in tensor memory, 4096 per issuing thread; the pipe needs n/2 cycles per MMA"
     return out
 
 

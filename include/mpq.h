@@ -258,7 +258,7 @@ int32_t mpq_weight_save(mpq_context* ctx, const mpq_weight* w, const char* path)
 int32_t mpq_weight_load(mpq_context* ctx, const char* path, mpq_weight** out);
 
 /* ---- measured ceilings ------------------------------------------------------ */
-/* Two probes for whoever reports roofline fractions of the kernels above (no counterpart in the
+/* Probes for whoever reports roofline fractions of the kernels above (no counterpart in the
  * reference; the caller times them with events on `stream`).
  * mpq_probe_hbm_read streams `bytes` of device memory once, read-only, with the loads the Q4 kernels
  * use (out_dev: a device word that is practically never written).  Use a buffer larger than L2.
@@ -266,6 +266,11 @@ int32_t mpq_weight_load(mpq_context* ctx, const char* path, mpq_weight** out);
  * (128 x 224 x 64) back to back from resident operands; *flop_out = the flop the launch executes. */
 int32_t mpq_probe_hbm_read(mpq_context* ctx, const void* buf_dev, int64_t bytes, uint32_t* out_dev, void* stream);
 int32_t mpq_probe_fp4_mma(mpq_context* ctx, int32_t mmas_per_sm, double* flop_out, void* stream);
+/* mpq_probe_f16_mma (synchronous; allocates a small result buffer): `issuers` threads of one CTA per SM (1..4, one per
+ * warp, each with its own accumulator) issue mmas_per_issuer tcgen05.mma.kind::f16 of 128 x n_cols x 16 with the A
+ * operand in tensor memory, as the Q4 tcgen05 kernel does; *cycles_per_mma = median over SMs of the SM cycles from
+ * first issue to completion / all MMAs issued on the SM (the tensor pipe needs n_cols / 2 cycles for one). */
+int32_t mpq_probe_f16_mma(mpq_context* ctx, int32_t n_cols, int32_t issuers, int32_t mmas_per_issuer, double* cycles_per_mma);
 
 #ifdef __cplusplus
 }

@@ -75,6 +75,7 @@ SIGNATURES = {
     "mpq_weight_load": (_i32, [_vp, C.c_char_p, _pp]),
     "mpq_probe_hbm_read": (_i32, [_vp, _vp, _i64, _vp, _vp]),
     "mpq_probe_fp4_mma": (_i32, [_vp, _i32, C.POINTER(C.c_double), _vp]),
+    "mpq_probe_f16_mma": (_i32, [_vp, _i32, _i32, _i32, C.POINTER(C.c_double)]),
 }
 
 _lib = None

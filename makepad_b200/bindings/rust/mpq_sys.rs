@@ -107,6 +107,7 @@ pub struct LibMpq {
     pub mpq_weight_load: unsafe extern "C" fn(*mut mpq_context, *const c_char, *mut *mut mpq_weight) -> i32,
     pub mpq_probe_hbm_read: unsafe extern "C" fn(*mut mpq_context, *const c_void, i64, *mut u32, *mut c_void) -> i32,
     pub mpq_probe_fp4_mma: unsafe extern "C" fn(*mut mpq_context, i32, *mut f64, *mut c_void) -> i32,
+    pub mpq_probe_f16_mma: unsafe extern "C" fn(*mut mpq_context, i32, i32, i32, *mut f64) -> i32,
     _keep_module_alive: *mut c_void,
 }
 
@@ -171,6 +172,7 @@ impl LibMpq {
                 mpq_weight_load: sym!(h, "mpq_weight_load"),
                 mpq_probe_hbm_read: sym!(h, "mpq_probe_hbm_read"),
                 mpq_probe_fp4_mma: sym!(h, "mpq_probe_fp4_mma"),
+                mpq_probe_f16_mma: sym!(h, "mpq_probe_f16_mma"),
                 _keep_module_alive: h,
             })
         }

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <vector>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -1548,6 +1549,39 @@ extern "C" int32_t mpq_probe_hbm_read(mpq_context* ctx, const void* buf_dev, int
     ctx->launches += 1;
     CU_TRY(ctx, cudaGetLastError());
     return MPQ_OK;
+}
+
+extern "C" int32_t mpq_probe_f16_mma(mpq_context* ctx, int32_t n_cols, int32_t issuers, int32_t mmas_per_issuer, double* cycles_per_mma)
+{
+    if (!ctx_ok(ctx)) return MPQ_ERR_INVALID_ARG;
+    if (!cycles_per_mma || n_cols < 16 || n_cols > 64 || n_cols % 16 || issuers < 1 || issuers > 4 || mmas_per_issuer < 4 || mmas_per_issuer > (1 << 20) || mmas_per_issuer % 4)
+        return fail(ctx, MPQ_ERR_INVALID_ARG, "probe wants n_cols in {16, 32, 48, 64}, 1..4 issuers, a multiple of 4 MMAs");
+    CU_TRY(ctx, cudaSetDevice(ctx->device));
+    int32_t st = q4_status_word(ctx);
+    if (st) return st;
+    const int sms = ctx->prop.multiProcessorCount;
+    long long* cyc = nullptr;
+    CU_TRY(ctx, cudaMalloc(&cyc, sizeof(long long) * sms));
+    const size_t smem = 8192 + 64 + 1024 + 116 * 1024;          // above half an SM's shared memory: one CTA per SM
+    static PerDeviceOnce configured;
+    if (configured.needs(ctx->device)) {
+        cudaError_t e = cudaFuncSetAttribute(q4u_mma_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaFree(cyc); return fail(ctx, MPQ_ERR_CUDA, "probe attribute: %s", cudaGetErrorString(e)); }
+        configured.mark(ctx->device);
+    }
+    std::vector<long long> host(sms);
+    cudaError_t e = cudaSuccess;
+    for (int rep = 0; rep < 2 && e == cudaSuccess; ++rep) {       // the second run is the measurement
+        q4u_mma_probe_kernel<<<sms, 128, smem>>>(n_cols, issuers, mmas_per_issuer / 4, cyc, ctx->q4_status);
+        ctx->launches += 1;
+        e = cudaDeviceSynchronize();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(host.data(), cyc, sizeof(long long) * sms, cudaMemcpyDeviceToHost);
+    cudaFree(cyc);
+    if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "probe: %s", cudaGetErrorString(e));
+    std::sort(host.begin(), host.end());
+    *cycles_per_mma = (double)host[sms / 2] / ((double)mmas_per_issuer * issuers);
+    return mpq_context_poll_status(ctx);
 }
 
 extern "C" int32_t mpq_probe_fp4_mma(mpq_context* ctx, int32_t mmas_per_sm, double* flop_out, void* stream)

@@ -638,4 +638,60 @@ __global__ void __launch_bounds__(256) q4u_reduce_kernel(const float* __restrict
     }
 }
 
+// ---------------------------------------------------------------------------
+// probe: how fast can `issuers` threads (one per warp, each with its own accumulator and A columns) issue
+// tcgen05.mma.kind::f16 of 128 x n_cols x 16 with A in tensor memory?  Per CTA the cycles from the first issue to the
+// completion of the last MMA of warp 0 go to cycles[blockIdx.x].  Operands are constants (1.0); nothing else runs.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128, 1) q4u_mma_probe_kernel(int n_cols, int issuers, int reps, long long* __restrict__ cycles,
+                                                                int* __restrict__ status)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    const uint32_t smem0 = (smem_u32(smem_dyn) + 1023u) & ~1023u;             // B tile: up to 64 rows x 128 bytes
+    const uint32_t bars = smem0 + 8192;
+    for (int i = threadIdx.x; i < 8192 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem_dyn + (smem0 - smem_u32(smem_dyn)))[i] = 0x3C003C00u;
+    if (threadIdx.x == 0) {
+        for (int w = 0; w < 4; ++w) q4u_bar_init(bars + 8 * w, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    q4u_fence_before();
+    __syncthreads();
+    q4u_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const uint32_t ones[8] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+        for (int c = 0; c < 128; c += 8) q4u_st8(tmem + ((uint32_t)(warp * 32) << 16) + Q4U_A_COL + c, ones);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    q4u_fence_before();
+    __syncthreads();
+    q4u_fence_after();
+    if (warp < issuers && lane == 0) {
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint64_t bd = q4u_desc_sw128(smem0);
+        const uint32_t d = tmem + (uint32_t)warp * 64, a = tmem + Q4U_A_COL + (uint32_t)warp * 32;
+        const long long t0 = clock64();
+        for (int r = 0; r < reps; ++r) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q4u_mma(d, a + j * 8, bd + 2 * j, idesc, (r > 0 || j > 0) ? 1u : 0u);
+        }
+        q4u_commit(bars + 8 * warp);
+        if (!q4u_bar_wait(bars + 8 * warp, 0)) atomicExch(status, 39);
+        if (warp == 0) cycles[blockIdx.x] = clock64() - t0;
+    }
+    q4u_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        q4u_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
 }  // namespace mpq

@@ -366,3 +366,16 @@ def test_error_statuses(ctx):
     assert lib.mpq_weight_destroy(w.h) == _lib.ERR_INVALID_ARG if w.h else True
     with pytest.raises(makepad_b200.MpqError):
         makepad_b200.Q4Weight(ctx, codes, scales[:, :1])
+
+
+def test_f16_mma_issue_probe(ctx):
+    """The probe behind the tcgen05 kernel's structure: several issuing threads get closer to the tensor pipe's rate
+    (n / 2 cycles per MMA of 128 x n x 16) than one does; the status word stays clean."""
+    cyc = C.c_double()
+    got = {}
+    for issuers in (1, 4):
+        ctx.check(ctx.lib.mpq_probe_f16_mma(ctx.h, 64, issuers, 1024, C.byref(cyc)))
+        got[issuers] = cyc.value
+    assert 31.0 <= got[4] < got[1] < 400.0, got
+    assert ctx.lib.mpq_probe_f16_mma(ctx.h, 24, 1, 1024, C.byref(cyc)) == _lib.ERR_INVALID_ARG
+    assert ctx.lib.mpq_context_poll_status(ctx.h) == _lib.OK
