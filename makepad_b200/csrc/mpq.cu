@@ -660,7 +660,7 @@ static int32_t q4_rect_forward(mpq_context* ctx, const Q4Dev& q, const Q4RectPla
     if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_rect_kernel launch failed: %s", cudaGetErrorString(e));
     if (pl.nks > 1) {
         cudaLaunchConfig_t cfg = {};
-        const int64_t total = (int64_t)M * q.N;
+        const int64_t total = ((int64_t)M * q.N + 3) / 4;              // four columns per thread where the shapes allow
         cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)ctx->prop.multiProcessorCount * 8));
         cfg.blockDim = dim3(256);
         cfg.stream = s;
