@@ -45,7 +45,7 @@ struct mpq_context {
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
-    int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, 1 or 2
+    int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, else 1..8
     uint2* q4_partials;
     int q4_partials_ctas;
     int* q4_status;
@@ -174,7 +174,7 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_RECT_DEPTH");
-    c->q4_rect_depth = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+    c->q4_rect_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_SLAB4");
     c->q4_slab4 = !(e && e[0] == '0');
     e = getenv("MPQ_Q4_TILE");
@@ -574,7 +574,7 @@ static bool q4_rect_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4RectPl
     // The deeper ring first (measured: two stages per warp with more K slices beat one stage with fewer);
     // MPQ_Q4_RECT_DEPTH pins the ring depth.
     bool found = false;
-    for (int depth = 2; depth >= 1; --depth) {
+    for (int depth = ctx->q4_rect_depth ? std::min(ctx->q4_rect_depth, (int)Q4S_MAX_DEPTH) : 2; depth >= 1; --depth) {
         if (ctx->q4_rect_depth && depth != ctx->q4_rect_depth) continue;
         const size_t ring = (size_t)Q4R_WARPS * depth * Q4R_STAGE_BYTES;
         if (ring + wpart + bars + per_chunk * Q4R_G > total) continue;
