@@ -21,7 +21,7 @@
 // stored to y directly, a batch cut into pieces goes through one partial slice per piece, which q4u_reduce_kernel
 // adds in piece order (deterministic).
 //
-// DATA FLOW per CTA (one per SM).  The CTA is four independent pipelines ("teams") fed by one producer; team t owns a
+// DATA FLOW per CTA (one per SM).  The CTA is four independent pipelines ("teams") fed by two producer warps; team t owns a
 // weight ring, an A-operand stage and an accumulator in tensor memory, and handles group t of the batch:
 //   warp 0          weight producer: cp.async.bulk of the weight units into the teams' rings (the same tile stream
 //                   every other Q4 kernel reads: no second copy of the weights), as far ahead as the rings allow:
@@ -33,8 +33,8 @@
 //   warps 5..20     expansion, four warps per team: thread = one weight row = one tensor-memory lane; shared memory
 //                   -> registers -> hi/lo fp16 -> tcgen05.st into the team's A stage (two halves with their own
 //                   hand-offs: one is filled while the MMAs of the other run); every Q4U_SEG chunks the
-//                   same warps add the team's accumulator (tcgen05.ld) to running fp32 sums in registers, and after
-//                   the piece's last chunk store them
+//                   same warps add the team's accumulator (tcgen05.ld) to running fp32 sums (thread-local memory,
+//                   touched once per segment), and after the piece's last chunk store them
 // Hand-offs are mbarriers; every wait is bounded (a wait that runs out sets the status word and every role
 // leaves its loop; tensor memory is freed on every path).  No TMA load uses multicast.
 #pragma once
