@@ -45,7 +45,6 @@ struct mpq_context {
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
-    int q4_xlanes_min;        // fewest ranks for which the fused all-reduce reads the ranks' copies side by side (0 = never)
     int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, else 1..8
     uint2* q4_partials;
     int q4_partials_ctas;
@@ -174,8 +173,6 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_umma_min = e ? atoi(e) : 17;         // measured: above 16 rows (two passes of the rectangle kernel) the tcgen05 kernel is faster
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
-    e = getenv("MPQ_Q4_XLANES_MIN");
-    c->q4_xlanes_min = e ? atoi(e) : 0;        // measured on two ranks: the one-after-the-other form is faster there
     e = getenv("MPQ_Q4_RECT_DEPTH");
     c->q4_rect_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_SLAB4");
@@ -456,10 +453,10 @@ static bool q4_stream_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4Stre
     return false;
 }
 
-template <int G, bool XLANES = false>
+template <int G>
 static cudaError_t q4_stream_launch_t(int device, const Q4StreamLaunch& p, int grid, size_t smem, bool pdl, cudaStream_t s)
 {
-    auto kern = q4_stream_kernel<G, XLANES>;
+    auto kern = q4_stream_kernel<G>;
     static PerDeviceOnce configured;                      // the attribute is per device, not per process
     if (configured.needs(device)) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - Q4S_STATIC_SMEM));
@@ -537,11 +534,7 @@ static int32_t q4_stream_enqueue(mpq_context* ctx, const Q4StreamPlan& pl, const
 #else
     const Q4StreamLaunch& p = p_in;
 #endif
-    // from q4_xlanes_min ranks the row-parallel sum reads the ranks' copies side by side (its own instantiation of the kernel)
-    const bool xl = p.xworld > 0 && ctx->q4_xlanes_min > 0 && p.xworld >= ctx->q4_xlanes_min;
-    cudaError_t e;
-    if (xl) e = pl.G == 2 ? q4_stream_launch_t<2, true>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1, true>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
-    else e = pl.G == 2 ? q4_stream_launch_t<2>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
+    cudaError_t e = pl.G == 2 ? q4_stream_launch_t<2>(ctx->device, p, grid, pl.smem, ctx->pdl, s) : q4_stream_launch_t<1>(ctx->device, p, grid, pl.smem, ctx->pdl, s);
     ctx->launches += 1;
     if (e != cudaSuccess) return fail(ctx, MPQ_ERR_CUDA, "q4_stream_kernel launch failed: %s", cudaGetErrorString(e));
     return MPQ_OK;

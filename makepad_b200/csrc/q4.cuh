@@ -756,10 +756,7 @@ __device__ __forceinline__ uint32_t q4s_stage_pass(const Q4StreamLaunch& p, int 
 }
 
 // dynamic shared memory: ring [16 warps][depth][G units] | xs | cs | mbarriers | wpart (the warps' parked partial tiles)
-// XLANES selects how the row-parallel sum at the end reads the ranks' copies (see there).  It is a template parameter and
-// not a run-time switch because the single-GPU instantiation must stay exactly as it is: every variant of that block tried
-// inside it moved the main loop's register allocation and cost 2 to 3 % of the decode rate.
-template <int G, bool XLANES = false>
+template <int G>
 __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const __grid_constant__ Q4StreamLaunch p)
 {
     constexpr int STAGE_BYTES = G * Q4_UNIT_BYTES;
@@ -1005,57 +1002,25 @@ __global__ void __launch_bounds__(Q4S_THREADS, 1) q4_stream_kernel(const __grid_
     // ---- row-parallel: add the ranks' partial outputs.  The tagged pairs need no flag and no grid
     // barrier: an element is ready when all xworld copies of it carry the tag.
     if (p.xworld > 0) {
-        if constexpr (XLANES) {
-            // Eight lanes per element, one per rank: the ranks' copies are requested side by side (one after the other,
-            // eight system-scope round trips to L2 cost more than a small shard's streaming), each lane polls only its
-            // own copy, and the sum is taken in rank order through shuffles whatever the order of arrival.
-            const uint2* mine = p.xmine;
-            const int total = p.M * p.N;
-            const int r = lane & 7, sub = lane >> 3;
-            for (int e0 = (blockIdx.x * (THREADS / 32) + warp) * 4; e0 < total; e0 += gridDim.x * (THREADS / 32) * 4) {
-                const int e = e0 + sub;
-                const bool active = e < total && r < p.xworld;
+        const uint2* mine = p.xmine;
+        const int total = p.M * p.N;
+        for (int e = blockIdx.x * THREADS + tid; e < total; e += gridDim.x * THREADS) {
+            float sum = 0.f;
+            bool ok = true;
+            for (int r = 0; r < p.xworld && ok; ++r) {
                 const uint2* src = mine + (size_t)r * p.xslot + e;
-                uint2 v = make_uint2(0u, 1u);
-                if (active) {
+                uint2 v = ld_tagged_sys(src);
+                for (uint32_t spin = 0; v.y != 1u && spin < p.xlimit; ++spin) {
+                    __nanosleep(64);
                     v = ld_tagged_sys(src);
-                    for (uint32_t spin = 0; v.y != 1u && spin < p.xlimit; ++spin) {
-                        __nanosleep(64);
-                        v = ld_tagged_sys(src);
-                    }
                 }
-                const bool ok = v.y == 1u;
-                if (active && ok) st_tagged_sys(const_cast<uint2*>(src), 0.f, 0u);      // consumed: free the slot
-                float sum = 0.f;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) sum += __shfl_sync(0xFFFFFFFFu, __uint_as_float(v.x), (lane & 24) + k);
-                if (!__all_sync(0xFFFFFFFFu, ok)) { if (lane == 0) atomicExch(p.status, 7); break; }   // a peer never delivered
-                if (r == 0 && e < total) {
-                    const int m = e / p.N;
-                    p.Y[(size_t)m * p.ldy + (e - m * p.N)] = sum;
-                }
+                ok = v.y == 1u;
+                sum += __uint_as_float(v.x);
+                if (ok) st_tagged_sys(const_cast<uint2*>(src), 0.f, 0u);      // consumed: free the slot
             }
-        } else {
-            const uint2* mine = p.xmine;
-            const int total = p.M * p.N;
-            for (int e = blockIdx.x * THREADS + tid; e < total; e += gridDim.x * THREADS) {
-                float sum = 0.f;
-                bool ok = true;
-                for (int r = 0; r < p.xworld && ok; ++r) {
-                    const uint2* src = mine + (size_t)r * p.xslot + e;
-                    uint2 v = ld_tagged_sys(src);
-                    for (uint32_t spin = 0; v.y != 1u && spin < p.xlimit; ++spin) {
-                        __nanosleep(64);
-                        v = ld_tagged_sys(src);
-                    }
-                    ok = v.y == 1u;
-                    sum += __uint_as_float(v.x);
-                    if (ok) st_tagged_sys(const_cast<uint2*>(src), 0.f, 0u);      // consumed: free the slot
-                }
-                if (!ok) { atomicExch(p.status, 7); break; }       // a peer never delivered: report it and leave
-                const int m = e / p.N;
-                p.Y[(size_t)m * p.ldy + (e - m * p.N)] = sum;
-            }
+            if (!ok) { atomicExch(p.status, 7); break; }       // a peer never delivered: report it and leave
+            const int m = e / p.N;
+            p.Y[(size_t)m * p.ldy + (e - m * p.N)] = sum;
         }
     }
 }
