@@ -50,6 +50,8 @@ constexpr int Q4U_MAX_WSTAGES = 8;            // weight ring PER TEAM: at most s
 constexpr int Q4U_WSTAGE_BYTES = 4 * Q4_UNIT_BYTES;
 constexpr int Q4U_XSTAGES = 4;                // activation ring: stages of one chunk (hi tile + lo tile)
 constexpr int Q4U_SEG = 16;                   // chunks (1024 of K) a team accumulates inside the tensor core before its sums are drained
+                                              // (measured on 8192 x 28672 at 64 rows: max error 1.4e-5 of the output rms with 16,
+                                              //  2.3e-5 with 32, 3.9e-5 with 64 and more: the bound the tests hold is 2e-5)
 constexpr int Q4U_A_COL = 256;                // accumulators: columns [0, 256), 64 per team; A stages: [256, 512), 64 per team
 constexpr uint32_t Q4U_SPIN = 1u << 22;       // tries of one mbarrier before giving up
 
