@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <vector>
 #include <cstdarg>
 #include <cstdio>
@@ -45,6 +46,7 @@ struct mpq_context {
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
+    int q4_rect_nks;          // experiment: at least so many K slices in the rectangle kernel (0 = the plan's choice)
     int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, else 1..8
     uint2* q4_partials;
     int q4_partials_ctas;
@@ -173,6 +175,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_umma_min = e ? atoi(e) : 17;         // measured: above 16 rows (two passes of the rectangle kernel) the tcgen05 kernel is faster
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_RECT_NKS");
+    c->q4_rect_nks = e ? atoi(e) : 0;
     e = getenv("MPQ_Q4_RECT_DEPTH");
     c->q4_rect_depth = (e && e[0] >= '1' && e[0] <= '8') ? e[0] - '0' : 0;
     e = getenv("MPQ_Q4_SLAB4");
@@ -569,7 +573,7 @@ static bool q4_rect_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4RectPl
     const int mt = (M + 3) / 4, mp = 4 * mt;
     const int sms = ctx->prop.multiProcessorCount;
     const size_t per_chunk = (size_t)2 * mp * 128 + (size_t)2 * mp * 8;          // fragments + corrections
-    const size_t wpart = (size_t)Q4R_WARPS * 2 * (4 * mt) * 32 * 4, bars = (size_t)Q4R_WARPS * Q4S_MAX_DEPTH * 8;
+    const size_t wpart = (size_t)Q4R_WARPS * (4 * mt) * 32 * 4, bars = (size_t)Q4R_WARPS * Q4S_MAX_DEPTH * 8;
     const size_t total = (size_t)227 * 1024 - 512;
     // The deeper ring first (measured: two stages per warp with more K slices beat one stage with fewer);
     // MPQ_Q4_RECT_DEPTH pins the ring depth.
@@ -579,11 +583,24 @@ static bool q4_rect_plan(const mpq_context* ctx, const Q4Dev& q, int M, Q4RectPl
         const size_t ring = (size_t)Q4R_WARPS * depth * Q4R_STAGE_BYTES;
         if (ring + wpart + bars + per_chunk * Q4R_G > total) continue;
         int max_slice = (int)((total - ring - wpart - bars) / per_chunk) / Q4R_G * Q4R_G;
-        // K slices: as few as fit, but enough of them that tile groups x slices can cover the SMs
-        int nks = (q.nchunks + max_slice - 1) / max_slice;
-        while (nks < 16 && (int64_t)q.nrp * nks * 10 < (int64_t)sms * 6 && q.nchunks / (nks + 1) >= 2 * Q4R_G) ++nks;
-        int slice = ((q.nchunks + nks - 1) / nks + Q4R_G - 1) / Q4R_G * Q4R_G;
-        nks = (q.nchunks + slice - 1) / slice;
+        // K slices.  More of them shorten what every CTA stages of x and lengthen the reduction of the slices, and the
+        // split has to divide the chunks and the tiles evenly over the SMs: the candidates' cost is estimated from measured
+        // rates (microseconds: main loop per tile and chunk by MMA tile count, staging per row and chunk, reduction per
+        // output element and slice) and the cheapest is taken.
+        const int nks_min = (q.nchunks + max_slice - 1) / max_slice;
+        const int nks_max = std::max(nks_min, std::min(16, q.nchunks / (2 * Q4R_G)));
+        static const double c_main[4] = {0.035, 0.050, 0.070, 0.089};
+        int nks = nks_min, slice = 0;
+        double best_cost = 1e30;
+        for (int cand = nks_min; cand <= nks_max; ++cand) {
+            if (ctx->q4_rect_nks > 0 && cand != std::min(std::max(ctx->q4_rect_nks, nks_min), nks_max)) continue;
+            const int sl = ((q.nchunks + cand - 1) / cand + Q4R_G - 1) / Q4R_G * Q4R_G;
+            const int real = (q.nchunks + sl - 1) / sl;
+            const int tg = std::max(1, std::min(q.nrp, sms / real));
+            const int tiles = (q.nrp + tg - 1) / tg;
+            const double cost = c_main[mt - 1] * tiles * sl + 0.012 * mp * sl + (real > 1 ? 5e-6 * real * (double)M * (double)q.N : 0.0);
+            if (cost < best_cost) { best_cost = cost; nks = real; slice = sl; }
+        }
         if (nks > sms) continue;                           // (cannot happen for K below a few million)
         if (found) continue;
         found = true;

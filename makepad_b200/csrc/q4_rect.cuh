@@ -68,7 +68,9 @@ __device__ __forceinline__ void q4r_stage_one(float4 v, int m, int f, float sc, 
     }
 }
 
-// dynamic shared memory: ring [16 warps][depth][2 units] | xs | cs | wpart [16 warps][2][4 MT][32] | mbarriers
+// dynamic shared memory: ring [16 warps][depth][2 units] | xs | cs | wpart [16 warps][4 MT][32] | mbarriers
+// (a warp parks the partial tile its run STARTS in in wpart; the one its run ENDS in goes to the start of its own ring,
+//  which is idle by then: the 16 KB that saves lets 8 rows x K = 4096 fit in one slice, with no reduction launch)
 template <int MT>
 __global__ void __launch_bounds__(Q4R_THREADS, 1) q4_rect_kernel(const __grid_constant__ Q4RectLaunch p)
 {
@@ -97,7 +99,11 @@ __global__ void __launch_bounds__(Q4R_THREADS, 1) q4_rect_kernel(const __grid_co
     const uint32_t cs_u32 = xs_u32 + (uint32_t)p.slice_chunks * 2 * MP * 128;
     const uint32_t wpart_u32 = cs_u32 + (uint32_t)p.slice_chunks * 2 * MP * 8;
     float* wpart = reinterpret_cast<float*>(smem_raw + (wpart_u32 - smem0));
-    const uint32_t bars_u32 = wpart_u32 + Q4R_WARPS * 2 * NV * 32 * 4 + (uint32_t)warp * Q4S_MAX_DEPTH * 8;
+    // parked partial tile (warp w, slot): slot 0 in wpart, slot 1 at the start of warp w's ring
+    auto parked = [&](int w, int slot) -> float* {
+        return slot == 0 ? wpart + (size_t)w * NV * 32 : reinterpret_cast<float*>(smem_raw + (size_t)w * D * Q4R_STAGE_BYTES);
+    };
+    const uint32_t bars_u32 = wpart_u32 + Q4R_WARPS * NV * 32 * 4 + (uint32_t)warp * Q4S_MAX_DEPTH * 8;
 
     if (lane == 0) {
         for (int s = 0; s < D; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bars_u32 + s * 8), "r"(1));
@@ -177,14 +183,23 @@ __global__ void __launch_bounds__(Q4R_THREADS, 1) q4_rect_kernel(const __grid_co
         const int m = i / pk4, f = i - m * pk4;
         q4r_stage_one(cache[it], m, f, sc, MP, xs_u32, cs_u32, lane);
     }
-    for (int i0 = Q4R_CACHE * Q4R_THREADS; i0 < total4; i0 += Q4R_THREADS) {
-        const int i = i0 + tid;
-        if (i0 + (tid & ~31) >= total4) break;
-        const int m = i / pk4, f = i - m * pk4;
-        const int64_t k = k0 + 4 * f;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (m < p.M && k < p.K) v = __ldg(reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + k));
-        q4r_stage_one(v, m, f, sc, MP, xs_u32, cs_u32, lane);
+    // what did not fit in the registers is read again, again Q4R_CACHE loads in flight per thread
+    for (int base = Q4R_CACHE * Q4R_THREADS; base < total4; base += Q4R_CACHE * Q4R_THREADS) {
+#pragma unroll
+        for (int it = 0; it < Q4R_CACHE; ++it) {
+            const int i = base + it * Q4R_THREADS + tid;
+            const int m = i / pk4, f = i - m * pk4;
+            const int64_t k = k0 + 4 * f;
+            cache[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < total4 && m < p.M && k < p.K) cache[it] = __ldg(reinterpret_cast<const float4*>(p.X + (size_t)m * p.K + k));
+        }
+#pragma unroll
+        for (int it = 0; it < Q4R_CACHE; ++it) {
+            const int i = base + it * Q4R_THREADS + tid;
+            if (base + it * Q4R_THREADS + (tid & ~31) >= total4) break;
+            const int m = i / pk4, f = i - m * pk4;
+            q4r_stage_one(cache[it], m, f, sc, MP, xs_u32, cs_u32, lane);
+        }
     }
     __syncthreads();
 
@@ -223,7 +238,7 @@ __global__ void __launch_bounds__(Q4R_THREADS, 1) q4_rect_kernel(const __grid_co
                         else p.partial[((size_t)ks * p.M + m) * p.N + n] = v;
                     }
                 } else {
-                    wpart[((warp * 2 + slot) * NV + bt * 4 + q) * 32 + lane] = v;
+                    parked(warp, slot)[(bt * 4 + q) * 32 + lane] = v;
                 }
             }
         if (!whole && lane == 0) wrp[warp][slot] = tile_rp;
@@ -310,7 +325,7 @@ __global__ void __launch_bounds__(Q4R_THREADS, 1) q4_rect_kernel(const __grid_co
         for (int i = 0; i < NV; ++i) v[i] = 0.f;
         for (; same; same &= same - 1u) {
             const int idx = __ffs(same) - 1;
-            const float* src = wpart + (size_t)idx * NV * 32 + lane;
+            const float* src = parked(idx >> 1, idx & 1) + lane;
 #pragma unroll
             for (int i = 0; i < NV; ++i) v[i] += src[i * 32];
         }
