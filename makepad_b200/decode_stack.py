@@ -91,11 +91,13 @@ class DecodeStack:
         self.launches_per_step = None          # counted by the library while the step is enqueued (capture())
         self.kernel_name = "q4_stream_kernel" if M <= 4 else "q4_stream_kernel (slabs of <= 4 rows) / q4_linear_kernel"
 
-    def _enqueue(self):
+    def _enqueue(self, first: int = 0, last: int = None):
         import torch
         s = C.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         lib, ctx = self.ctx.lib, self.ctx
         for i, w in enumerate(self.weights):
+            if i < first or (last is not None and i >= last):
+                continue
             xp = self.x.data_ptr() + 4 * self.x_off[i]
             yp = self.y.data_ptr() + 4 * self.y_off[i]
             ctx.check(lib.mpq_q4_linear_forward(ctx.h, w.h, C.c_void_p(xp), self.M, C.c_void_p(yp), s))
@@ -112,6 +114,30 @@ class DecodeStack:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, stream=self.stream):
             self._enqueue()
+        # The host-to-host step as one graph of its own: the layers' inputs are copied up in three parts (layer 0; layers
+        # 1..3; the rest), each part on a second stream beside the launches of the part before it, so that only the first
+        # 93 KB are waited for; the last output is read back at the end.
+        n0 = len(self.shapes)
+        bounds = sorted({0, min(1, self.layers), min(4, self.layers), self.layers})          # in layers
+        parts = [(bounds[i] * n0, bounds[i + 1] * n0) for i in range(len(bounds) - 1)]         # in projections
+        xend = lambda j: self.x_off[j] if j < len(self.weights) else self.x.numel()
+        side = torch.cuda.Stream(device=self.dev)
+        last = self.weights[-1]
+        self.graph_host = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_host, stream=self.stream):
+            cur = torch.cuda.current_stream(self.dev)
+            a0, a1 = xend(parts[0][0]), xend(parts[0][1])
+            self.x[a0:a1].copy_(self.x_host[a0:a1], non_blocking=True)
+            for k, (p0, p1) in enumerate(parts):
+                if k + 1 < len(parts):                               # the next part's inputs travel while this part runs
+                    b0, b1 = xend(parts[k + 1][0]), xend(parts[k + 1][1])
+                    side.wait_stream(cur)
+                    with torch.cuda.stream(side):
+                        self.x[b0:b1].copy_(self.x_host[b0:b1], non_blocking=True)
+                self._enqueue(p0, p1)
+                if k + 1 < len(parts):
+                    cur.wait_stream(side)
+            self.y_last_host.copy_(self.y[self.y_off[-1]:self.y_off[-1] + self.M * last.N], non_blocking=True)
         return self
 
     def step(self):
@@ -119,14 +145,12 @@ class DecodeStack:
         self.graph.replay()
 
     def step_host(self):
-        """One decode step from HOST activations to a HOST result: pinned H2D of every projection's
-        input, the 128 launches, D2H of the last projection's output, synchronise."""
+        """One decode step from HOST activations to a HOST result: pinned H2D of every projection's input (in three parts,
+        each copied beside the launches of the part before it), the 128 launches, D2H of the last projection's output,
+        synchronise."""
         import torch
         with torch.cuda.stream(self.stream):
-            self.x.copy_(self.x_host, non_blocking=True)
-            self.graph.replay()
-            last = self.weights[-1]
-            self.y_last_host.copy_(self.y[self.y_off[-1]:self.y_off[-1] + self.M * last.N], non_blocking=True)
+            self.graph_host.replay()
         self.stream.synchronize()
         return self.y_last_host
 
