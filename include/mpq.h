@@ -118,9 +118,10 @@ int32_t mpq_weight_destroy(mpq_weight* w);
 /* Forward calls on one context share that context's scratch buffers: issue
  * them in stream order (one stream per context at a time).
  * Y[M][N] = X[M][K] . W^T, fp32 in, fp32 accumulate, fp32 out.  X and Y are
- * row-major device arrays, 16-byte aligned.  Any M >= 1: M <= 4 is one
- * launch of the streaming kernel; 5..16 rows one pass of the rectangle kernel
- * (weights read once) plus a small reduction; from 17 rows slabs of up to 64
+ * row-major device arrays, 16-byte aligned.  Any M >= 1: one row, and up to
+ * four rows while M * K < 16384, is one launch of the streaming kernel; up to
+ * 16 rows otherwise one pass of the rectangle kernel (weights read once,
+ * only a K slice of x staged per CTA) plus a small reduction; from 17 rows slabs of up to 64
  * rows through the tcgen05 kernel (activation staging, main kernel, reduction
  * of the pieces).  The first call that needs a scratch buffer (or a larger
  * one) allocates it: make a warm-up call with the largest M before capturing
@@ -198,8 +199,9 @@ int32_t mpq_q4_linear_forward_allreduce(mpq_context* ctx, const mpq_weight* w, m
  * correctly rounded division.  F must be a multiple of 4; 16-byte aligned pointers. */
 int32_t mpq_swiglu(mpq_context* ctx, const float* gate_up_dev, int64_t M, int64_t F, float* out_dev, void* stream);
 /* Y[M][N] = swiglu(gate_up)[M][K] * W^T with gate_up[M][2K]: the down projection with the SwiGLU fused into
- * the kernel's activation staging (M <= 4: the intermediate never exists in memory; larger M run
- * mpq_swiglu into scratch the context owns, then mpq_q4_linear_forward).  Same bits as the two calls. */
+ * the kernel's activation staging where mpq_q4_linear_forward would use the streaming kernel (one row, or
+ * up to four rows of a short K: the intermediate never exists in memory); otherwise mpq_swiglu runs into
+ * scratch the context owns, then mpq_q4_linear_forward.  Same bits as the two calls. */
 int32_t mpq_q4_linear_forward_swiglu(mpq_context* ctx, const mpq_weight* w, const float* gate_up_dev, int64_t M,
                                      float* y_dev, void* stream);
 

@@ -46,6 +46,7 @@ struct mpq_context {
     float* q4_rect_partial;   // [K slices][M][N] partial outputs of the rectangle kernel (grown on demand)
     size_t q4_rect_partial_bytes;
     bool q4_rect;             // use the rectangle kernel for 5..16 rows (else slabs of <= 4 rows through the streaming kernel)
+    int q4_stream_max_m;      // most activation rows mpq_q4_linear_forward gives to the streaming kernel (1..4)
     int q4_rect_nks;          // experiment: at least so many K slices in the rectangle kernel (0 = the plan's choice)
     int q4_rect_depth;        // ring depth of the rectangle kernel: 0 = choose, else 1..8
     uint2* q4_partials;
@@ -175,6 +176,8 @@ extern "C" int32_t mpq_context_create(int32_t device, mpq_context** out)
     c->q4_umma_min = e ? atoi(e) : 17;         // measured: above 16 rows (two passes of the rectangle kernel) the tcgen05 kernel is faster
     e = getenv("MPQ_Q4_RECT");
     c->q4_rect = !(e && e[0] == '0');
+    e = getenv("MPQ_Q4_STREAM_MAX_M");
+    c->q4_stream_max_m = (e && e[0] >= '1' && e[0] <= '4') ? e[0] - '0' : 4;
     e = getenv("MPQ_Q4_RECT_NKS");
     c->q4_rect_nks = e ? atoi(e) : 0;
     e = getenv("MPQ_Q4_RECT_DEPTH");
@@ -800,12 +803,21 @@ static int32_t q4_umma_forward(mpq_context* ctx, const Q4Dev& q, const float* x,
     return MPQ_OK;
 }
 
+// The streaming kernel stages ALL of x in every CTA, the rectangle kernel only a K slice of it: measured on the 7B shapes,
+// from about 16 K staged elements (4 rows of K = 4096, 2 rows of K = 11008) the rectangle kernel is the faster one for
+// several rows (4096 x 11008 at 4 rows: 11.9 against 22.8 us).  One row always streams.
+static bool q4_prefers_stream(const mpq_context* ctx, const Q4Dev& q, int64_t M)
+{
+    if (M > ctx->q4_stream_max_m) return false;
+    return M == 1 || !ctx->q4_rect || M * q.K < 16384;
+}
+
 // One launch for a slab of M <= 16 activation rows.
 static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s);
 static int32_t q4_forward_slab(mpq_context* ctx, const Q4Dev& q, const float* x, int M, float* y, int64_t ldy, cudaStream_t s)
 {
     Q4StreamPlan pl;
-    if (M <= 4 && q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
+    if (q4_prefers_stream(ctx, q, M) && q4_stream_plan(ctx, q, M, &pl)) return q4_stream_forward(ctx, q, pl, x, M, y, ldy, nullptr, s);
     Q4RectPlan rp;
     if (ctx->q4_rect && q4_rect_plan(ctx, q, M, &rp)) return q4_rect_forward(ctx, q, rp, x, M, y, ldy, s);
     return q4_forward_general(ctx, q, x, M, y, ldy, s);
@@ -846,7 +858,7 @@ static int32_t q4_forward_general(mpq_context* ctx, const Q4Dev& q, const float*
 static int q4_slab_rows(const mpq_context* ctx, const Q4Dev& q, int64_t M)
 {
     Q4StreamPlan pl;
-    if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) return (int)M;      // one launch of the streaming kernel
+    if (q4_prefers_stream(ctx, q, M) && q4_stream_plan(ctx, q, (int)M, &pl)) return (int)M;      // one launch of the streaming kernel
     if (ctx->q4_rect) return 16;
     if (ctx->q4_slab4 && M > 1) {
         const int widths[3] = {4, 2, 1};
@@ -948,7 +960,7 @@ extern "C" int32_t mpq_q4_linear_forward_swiglu(mpq_context* ctx, const mpq_weig
     const Q4Dev& q = w->q4;
     cudaStream_t s = (cudaStream_t)stream;
     Q4StreamPlan pl;
-    if (M <= 4 && q4_stream_plan(ctx, q, (int)M, &pl)) {
+    if (q4_prefers_stream(ctx, q, M) && q4_stream_plan(ctx, q, (int)M, &pl)) {
         Q4StreamLaunch p;
         const int grid = q4_stream_params(ctx, q, pl, gate_up_dev, (int)M, y_dev, q.N, &p);
         if ((st = q4_stream_scratch(ctx, grid))) return st;

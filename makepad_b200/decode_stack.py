@@ -89,7 +89,8 @@ class DecodeStack:
         self.graph = None
         self.bytes_per_step = layers * sum(q4_bytes(N, K, M) for (_, N, K) in shapes)
         self.launches_per_step = None          # counted by the library while the step is enqueued (capture())
-        self.kernel_name = "q4_stream_kernel" if M <= 4 else "q4_stream_kernel (slabs of <= 4 rows) / q4_linear_kernel"
+        self.kernel_name = ("q4_stream_kernel" if M == 1 else
+                            "q4_stream_kernel (up to 4 rows of a short K) / q4_rect_kernel (up to 16 rows) / q4_umma_kernel (from 17 rows)")
 
     def _enqueue(self, first: int = 0, last: int = None):
         import torch

@@ -39,9 +39,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(orc):
             assert int(status.item()) == 0
             ref = orc.q4_matmul_f64(codes, scales, x.cpu().numpy())
             assert torch.equal(outs[0], outs[1])                     # the second call found the array as clean as the first
-            if M <= 4:                                               # the same kernel, the same split into runs: the same bits
-                assert torch.equal(outs[0], want)
-            else:                                                    # other kernels above four rows: equal to rounding
+            if M == 1 or (M <= 4 and M * K < 16384):                 # the ordinary entry point streams too (one row; several rows
+                assert torch.equal(outs[0], want)                    # of a short K): the same kernel, the same runs, the same bits
+            else:                                                    # other kernels there: equal to rounding
                 rms = float(np.sqrt(np.mean(ref * ref)))
                 assert (outs[0] - want).abs().max().item() < 2e-5 * rms
             assert orc.rel_err(want.cpu().numpy(), ref)[1] < 1e-3
