@@ -111,6 +111,21 @@ impl<'c> QuantLinear<'c> {
         })
     }
 
+    /// Q4 without any allocation by the library (static device scratch; launches beyond its 512 CTAs are refused).
+    /// `status_dev`, when not null, is a caller-owned device int a kernel sets when one of its bounded waits runs out.
+    pub fn forward_q4_static(&self, x: DevicePtr, m: i64, y: DevicePtr, status_dev: DevicePtr, stream: *mut c_void) -> Result<(), MpqError> {
+        let c = self.weight.ctx;
+        c.check(unsafe {
+            (c.lib.mpq_q4_linear_forward_static)(c.raw, self.weight.raw, x.0 as *const f32, m, y.0 as *mut f32, status_dev.0 as *mut i32, stream)
+        })
+    }
+
+    /// Q4 down projection with SwiGLU in front: y = (silu(gate) * up) . W^T for gate_up[M][2K] = [gate | up] on the device.
+    pub fn forward_q4_swiglu(&self, gate_up: DevicePtr, m: i64, y: DevicePtr, stream: *mut c_void) -> Result<(), MpqError> {
+        let c = self.weight.ctx;
+        c.check(unsafe { (c.lib.mpq_q4_linear_forward_swiglu)(c.raw, self.weight.raw, gate_up.0 as *const f32, m, y.0 as *mut f32, stream) })
+    }
+
     /// Host-buffer convenience path (copies in, runs, copies out, synchronises).
     pub fn forward_q4_host(&self, x: &[f32], m: i64, y: &mut [f32]) -> Result<(), MpqError> {
         let c = self.weight.ctx;
@@ -119,4 +134,17 @@ impl<'c> QuantLinear<'c> {
         }
         c.check(unsafe { (c.lib.mpq_q4_linear_forward_host)(c.raw, self.weight.raw, x.as_ptr(), m, y.as_mut_ptr()) })
     }
+}
+
+/// Activations for the NVFP4 GEMM, quantised on the device: x[M][K] (fp32, or bf16 bits) -> codes [M][K/2], sf [M][K/16].
+/// With `swiglu` the input is [M][2K] = [gate | up] and silu(gate) * up is what gets quantised.
+pub fn nvfp4_quantize(ctx: &Context, x: DevicePtr, x_is_bf16: bool, swiglu: bool, m: i64, k: i64, tensor_scale: f32, codes: DevicePtr,
+                      sf: DevicePtr, stream: *mut c_void) -> Result<(), MpqError> {
+    let f = if swiglu { ctx.lib.mpq_nvfp4_quantize_swiglu } else { ctx.lib.mpq_nvfp4_quantize_activations };
+    ctx.check(unsafe { f(ctx.raw, x.0 as *const c_void, x_is_bf16 as i32, m, k, tensor_scale, codes.0 as *mut u8, sf.0 as *mut u8, stream) })
+}
+
+/// out[M][F] = silu(gate) * up for gate_up[M][2F] = [gate | up], fp32 on the device.
+pub fn swiglu(ctx: &Context, gate_up: DevicePtr, m: i64, f: i64, out: DevicePtr, stream: *mut c_void) -> Result<(), MpqError> {
+    ctx.check(unsafe { (ctx.lib.mpq_swiglu)(ctx.raw, gate_up.0 as *const f32, m, f, out.0 as *mut f32, stream) })
 }
